@@ -1,0 +1,271 @@
+"""CPU oracle for the attention-with-scores family.  TEST INFRASTRUCTURE ONLY.
+
+This module is the checker the CUDA kernels are compared against.  It is a
+plain fp32 restatement (torch CPU ops, no custom kernels) of the reference's
+own PyTorch oracle and of the derivations its verifier applies to that oracle:
+
+* ``naive_attention_with_scores``   follows reference_implementations.py:11-52
+* ``row_sum``                       follows benchmark.py:1528-1534
+* ``col_sum``                       follows benchmark.py:1575-1581
+* ``cross_token_qk_sum``            follows benchmark.py:1687-1693
+* ``cross_token_softmax_sum``       follows benchmark.py:1627-1646 (true -inf
+                                    instead of the -6e4 stand-in; identical in fp32)
+* ``softmax_col_sum``               softmax(scores, -1).sum(-2); the reference
+                                    verifier never checks this quantity
+                                    (benchmark.py:1352 stores it, nothing reads it)
+* ``log_normalizer``                flash.py:486  (L = m*sm_scale + log(l))
+* ``group_sum``                     the (B,Hk,.) layout the reference kernels
+                                    return because their output pointer is
+                                    offset by the kv head (attention_with_col_sum.py:72)
+
+Parity pin: ``tests/golden/*.npz`` were produced by importing the reference's
+``reference_implementations.naive_attention_with_scores`` (see
+``tests/golden/make_golden.py``) and ``tests/test_oracle.py`` checks this
+restatement against them bit for bit.  Quantities the reference's own checks
+never exercise (GQA group sums, softmax column sums, M != N, non-causal) are
+"parity unpinned" by the reference; they are pinned here only through the
+stored reference scores tensor and the formulas above.
+
+Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / reference
+legs may import this module.  The product package never does.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+NEG_INF_BITS = 0xFF800000
+
+
+def _expand_kv(x: torch.Tensor, groups: int) -> torch.Tensor:
+    return x if groups == 1 else torch.repeat_interleave(x, repeats=groups, dim=1)
+
+
+def causal_mask(M: int, N: int, p_seq: int = 0) -> torch.Tensor:
+    """True where key j is hidden from query i, i.e. j > i + p_seq.
+
+    p_seq = 0 is the reference oracle's top-left mask
+    (reference_implementations.py:36-40, torch.triu(diagonal=1)); p_seq = N - M
+    is the kernels' bottom-right alignment (flash.py:451).  Equal when M == N.
+    """
+    i = torch.arange(M).unsqueeze(1)
+    j = torch.arange(N).unsqueeze(0)
+    return j > (i + p_seq)
+
+
+def naive_attention_with_scores(q, k, v, causal, sm_scale=None, p_seq=0):
+    """(out, scores) in fp32 from inputs upcast to fp32.
+
+    scores = q @ k^T * sm_scale with -inf at masked entries; out =
+    softmax(scores) @ v.  Rows with no visible key give out = 0 (the kernels'
+    behaviour, flash.py:480-483) instead of NaN.
+    """
+    q = q.float()
+    k = k.float()
+    v = v.float()
+    B, Hq, M, D = q.shape
+    Hk, N = k.shape[1], k.shape[2]
+    assert Hq % Hk == 0
+    g = Hq // Hk
+    k = _expand_kv(k, g)
+    v = _expand_kv(v, g)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    scores = torch.matmul(q, k.transpose(-2, -1)) * sm_scale
+    if causal:
+        scores = scores.masked_fill(causal_mask(M, N, p_seq), float("-inf"))
+    w = torch.softmax(scores, dim=-1)
+    w = torch.nan_to_num(w, nan=0.0)
+    out = torch.matmul(w, v)
+    return out, scores
+
+
+def _zero_masked(scores):
+    return torch.where(torch.isneginf(scores), torch.zeros_like(scores), scores)
+
+
+def row_sum(scores):
+    """(B,Hq,M): sum over visible keys of the scaled raw score."""
+    return _zero_masked(scores).sum(dim=-1)
+
+
+def col_sum(scores):
+    """(B,Hq,N): sum over visible queries of the scaled raw score."""
+    return _zero_masked(scores).sum(dim=-2)
+
+
+def softmax_weights(scores):
+    return torch.nan_to_num(torch.softmax(scores, dim=-1), nan=0.0)
+
+
+def softmax_col_sum(scores):
+    """(B,Hq,N): column sums of the softmax weights."""
+    return softmax_weights(scores).sum(dim=-2)
+
+
+def cross_token_qk_sum(scores, split):
+    """(B,Hq,split): raw-score sums of queries >= split into keys < split."""
+    return _zero_masked(scores)[:, :, split:, :split].sum(dim=-2)
+
+
+def cross_token_softmax_sum(scores, split):
+    """(B,Hq,split): softmax-weight sums of queries >= split into keys < split."""
+    return softmax_weights(scores)[:, :, split:, :split].sum(dim=-2)
+
+
+def log_normalizer(scores):
+    """(B,Hq,M): logsumexp of the scaled scores; -inf for empty rows."""
+    return torch.logsumexp(scores, dim=-1)
+
+
+def group_sum(x, Hk):
+    """(B,Hq,L) -> (B,Hk,L): sum the G = Hq/Hk query heads sharing a kv head."""
+    B, Hq, L = x.shape
+    return x.view(B, Hk, Hq // Hk, L).sum(dim=2)
+
+
+# ---------------------------------------------------------------------------
+# O(S*D) known-answer identities for the raw sums (no S^2 tensor needed).
+# With visible(i) = {j <= i + p_seq} (causal) or all j:
+#   col_sum_j = sm_scale * k_j . sum_{i visible to j} q_i
+#   row_sum_i = sm_scale * q_i . sum_{j visible to i} k_j
+# ---------------------------------------------------------------------------
+
+def linear_col_sum(q, k, causal, sm_scale=None, p_seq=0, i_begin=0, n_end=None):
+    """fp64 (B,Hq,n_end) raw column sums over queries i >= i_begin."""
+    q = q.double()
+    k = k.double()
+    B, Hq, M, D = q.shape
+    Hk, N = k.shape[1], k.shape[2]
+    n_end = N if n_end is None else n_end
+    k = _expand_kv(k, Hq // Hk)[:, :, :n_end]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    qz = q.clone()
+    qz[:, :, :i_begin] = 0
+    if causal:
+        # suffix[i] = sum_{i' >= i} q_i'; key j sees queries i >= max(j - p_seq, 0)
+        suffix = torch.flip(torch.cumsum(torch.flip(qz, dims=[2]), dim=2), dims=[2])
+        suffix = torch.cat([suffix, torch.zeros_like(suffix[:, :, :1])], dim=2)
+        first = (torch.arange(n_end) - p_seq).clamp(min=0, max=M)
+        qs = suffix[:, :, first]
+    else:
+        qs = qz.sum(dim=2, keepdim=True).expand(B, Hq, n_end, D)
+    return (k * qs).sum(-1) * sm_scale
+
+
+def linear_row_sum(q, k, causal, sm_scale=None, p_seq=0):
+    """fp64 (B,Hq,M) raw row sums."""
+    q = q.double()
+    k = k.double()
+    B, Hq, M, D = q.shape
+    Hk, N = k.shape[1], k.shape[2]
+    k = _expand_kv(k, Hq // Hk)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    if causal:
+        prefix = torch.cumsum(k, dim=2)
+        prefix = torch.cat([torch.zeros_like(prefix[:, :, :1]), prefix], dim=2)
+        cnt = (torch.arange(M) + p_seq + 1).clamp(min=0, max=N)
+        ks = prefix[:, :, cnt]
+    else:
+        ks = k.sum(dim=2, keepdim=True).expand(B, Hq, M, D)
+    return (q * ks).sum(-1) * sm_scale
+
+
+# ---------------------------------------------------------------------------
+# Tolerances (written once, used by every parity test).
+#   out                      : max abs <= 2e-3
+#   scores                   : |x-ref| <= 1e-3*|ref| + 1e-4, masked entries bit-exact
+#   sums (fp32 accumulation) : |x-ref| <= 1e-3*|ref| + 1e-3*rms(ref)
+# ---------------------------------------------------------------------------
+OUT_ATOL = 2e-3
+REL_TOL = 1e-3
+SCORES_ATOL = 1e-4
+
+
+def check_out(x, ref):
+    err = (x.float() - ref.float()).abs().max().item()
+    return err <= OUT_ATOL, err
+
+
+def check_sum(x, ref):
+    x = x.double()
+    ref = ref.double()
+    atol = REL_TOL * ref.pow(2).mean().sqrt().item()
+    viol = (x - ref).abs() - (REL_TOL * ref.abs() + atol)
+    return bool((viol <= 0).all()), viol.max().item()
+
+
+def check_scores(x, ref, masked_bits=NEG_INF_BITS):
+    """Masked set identical and bit-exact fill; finite entries within tolerance."""
+    x = x.float()
+    ref = ref.float()
+    hidden = torch.isneginf(ref)
+    xb = x.contiguous().view(torch.int32)
+    fill = masked_bits - (1 << 32) if masked_bits >= (1 << 31) else masked_bits
+    ok_mask = bool((xb[hidden] == fill).all())
+    if masked_bits == NEG_INF_BITS:
+        ok_mask = ok_mask and bool((torch.isneginf(x) == hidden).all())
+    xv, rv = x[~hidden], ref[~hidden]
+    viol = (xv - rv).abs() - (REL_TOL * rv.abs() + SCORES_ATOL)
+    ok_val = bool((viol <= 0).all()) if xv.numel() else True
+    return ok_mask and ok_val, (viol.max().item() if xv.numel() else 0.0), ok_mask
+
+
+# ---------------------------------------------------------------------------
+# Seeded synthetic inputs with the shapes and value distributions of the five
+# benchmark configurations (random tensors, as the reference's own benchmark
+# uses: benchmark.py:281-283).
+# ---------------------------------------------------------------------------
+CONFIGS = {
+    "cfg1": dict(B=1, Hq=8, Hk=8, S=512, D=64, dtype="float16", causal=True, v="normal", vscale=1.0, split=None),
+    "cfg2": dict(B=1, Hq=32, Hk=32, S=1024, D=128, dtype="float16", causal=True, v="normal", vscale=1.0, split=None),
+    "cfg3": dict(B=1, Hq=28, Hk=4, S=4096, D=128, dtype="bfloat16", causal=True, v="normal", vscale=0.5, split=None),
+    "cfg4": dict(B=2, Hq=32, Hk=8, S=4096, D=128, dtype="float16", causal=True, v="normal", vscale=1.0, split=3072),
+    "cfg5": dict(B=4, Hq=32, Hk=8, S=16384, D=128, dtype="bfloat16", causal=False, v="uniform", vscale=1.0, split=12288),
+}
+
+
+def make_unit_inputs(cfg: dict, unit: int, seed: int = 0, S: int | None = None):
+    """q (1,G,S,D), k, v (1,1,S,D) of shard unit ``unit`` = b*Hk + hk.
+
+    Drawn in fp32 on the CPU from ``seed + unit`` and cast to the config's
+    dtype, so any rank (and the oracle) can rebuild any unit independently.
+    """
+    S = cfg["S"] if S is None else S
+    G = cfg["Hq"] // cfg["Hk"]
+    D = cfg["D"]
+    dt = getattr(torch, cfg["dtype"])
+    g = torch.Generator().manual_seed(seed + unit)
+    q = torch.randn(1, G, S, D, generator=g)
+    k = torch.randn(1, 1, S, D, generator=g)
+    if cfg["v"] == "uniform":
+        v = torch.rand(1, 1, S, D, generator=g) * 2 - 1
+    else:
+        v = torch.randn(1, 1, S, D, generator=g) * cfg["vscale"]
+    return q.to(dt), k.to(dt), v.to(dt)
+
+
+def make_inputs(cfg: dict, seed: int = 0, S: int | None = None, units=None):
+    """Full (B,Hq,S,D)/(B,Hk,S,D) tensors assembled from per-unit draws."""
+    B, Hk = cfg["B"], cfg["Hk"]
+    G = cfg["Hq"] // Hk
+    units = range(B * Hk) if units is None else units
+    qs, ks, vs = [], [], []
+    for u in units:
+        q, k, v = make_unit_inputs(cfg, u, seed, S)
+        qs.append(q)
+        ks.append(k)
+        vs.append(v)
+    n = len(qs)
+    if n == B * Hk:
+        q = torch.cat(qs, 1).view(B, Hk * G, *qs[0].shape[2:])
+        k = torch.cat(ks, 1).view(B, Hk, *ks[0].shape[2:])
+        v = torch.cat(vs, 1).view(B, Hk, *vs[0].shape[2:])
+    else:
+        q = torch.cat(qs, 1)
+        k = torch.cat(ks, 1)
+        v = torch.cat(vs, 1)
+    return q.contiguous(), k.contiguous(), v.contiguous()
