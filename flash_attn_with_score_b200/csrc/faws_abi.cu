@@ -1,0 +1,329 @@
+// extern "C" entry points declared in include/faws.h: argument validation,
+// workspace carving, kernel-family selection and the launch sequences.
+#include <atomic>
+#include <cstdio>
+
+#include "faws_internal.cuh"
+
+namespace faws {
+
+static std::atomic<int64_t> g_launches{0};
+static thread_local int t_last_backend = 0;
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+int validate(const faws_problem* p) {
+  if (p == nullptr) return FAWS_EINVAL;
+  if (p->B <= 0 || p->Hq <= 0 || p->Hk <= 0 || p->M <= 0 || p->N <= 0) return FAWS_EINVAL;
+  if (p->Hq % p->Hk != 0) return FAWS_EINVAL;
+  if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128) return FAWS_EUNSUPPORTED;
+  if (p->dtype != FAWS_FP16 && p->dtype != FAWS_BF16) return FAWS_EUNSUPPORTED;
+  if (p->m_begin < 0 || p->m_end > p->M || p->m_begin > p->m_end) return FAWS_EINVAL;
+  if (p->q.ptr == nullptr || p->k.ptr == nullptr) return FAWS_EINVAL;
+  if (p->backend < FAWS_BACKEND_AUTO || p->backend > FAWS_BACKEND_TCGEN05) return FAWS_EINVAL;
+  return FAWS_OK;
+}
+
+FwdParams make_fwd(const faws_problem* p) {
+  FwdParams f{};
+  f.q = p->q.ptr; f.k = p->k.ptr; f.v = p->v.ptr; f.o = p->out.ptr;
+  f.q_sb = p->q.stride_b; f.q_sh = p->q.stride_h; f.q_ss = p->q.stride_s;
+  f.k_sb = p->k.stride_b; f.k_sh = p->k.stride_h; f.k_ss = p->k.stride_s;
+  f.v_sb = p->v.stride_b; f.v_sh = p->v.stride_h; f.v_ss = p->v.stride_s;
+  f.o_sb = p->out.stride_b; f.o_sh = p->out.stride_h; f.o_ss = p->out.stride_s;
+  f.L = p->log_normalizer;
+  f.B = p->B; f.Hq = p->Hq; f.Hk = p->Hk; f.G = p->Hq / p->Hk;
+  f.M = p->M; f.N = p->N; f.D = p->D;
+  f.p_seq = p->N - p->M;
+  f.m_begin = p->m_begin; f.m_end = p->m_end;
+  f.causal = p->causal ? 1 : 0;
+  f.sm_scale = p->sm_scale;
+  f.schedule = kForward;
+  f.masked_bits = 0xff800000u;
+  f.scores_f32 = 1;
+  return f;
+}
+
+ColSoftmaxParams make_cs(const faws_problem* p, const float* L, float* out, int i_begin, int n_end) {
+  ColSoftmaxParams c{};
+  c.q = p->q.ptr; c.k = p->k.ptr;
+  c.q_sb = p->q.stride_b; c.q_sh = p->q.stride_h; c.q_ss = p->q.stride_s;
+  c.k_sb = p->k.stride_b; c.k_sh = p->k.stride_h; c.k_ss = p->k.stride_s;
+  c.L = L; c.out = out;
+  c.B = p->B; c.Hq = p->Hq; c.Hk = p->Hk; c.G = p->Hq / p->Hk;
+  c.M = p->M; c.N = p->N; c.D = p->D;
+  c.p_seq = p->N - p->M; c.m_begin = p->m_begin; c.m_end = p->m_end;
+  c.causal = p->causal ? 1 : 0; c.sm_scale = p->sm_scale;
+  c.i_begin = i_begin; c.n_end = n_end;
+  return c;
+}
+
+// Runs the forward kernel on the family that fits; reports which one ran.
+int run_fwd(const faws_problem* p, FwdParams& f, cudaStream_t s, int* block_m, int* block_n) {
+  if (f.v == nullptr || f.o == nullptr) return FAWS_EINVAL;
+  bool use_tc = false;
+  if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_fwd_supported(f, p->dtype);
+  if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
+  *block_m = use_tc ? kTcBlockM : kGenericBlockM;
+  *block_n = use_tc ? kTcBlockN : kGenericBlockN;
+  if (f.col_partial != nullptr) {
+    f.ncols_pad = cdiv(f.col_n_end, 128) * 128;
+    f.qb_first = (f.col_row_begin > f.m_begin ? f.col_row_begin : f.m_begin) / *block_m;
+    f.n_qb_part = cdiv(f.m_end, *block_m) - f.qb_first;
+    if (f.n_qb_part < 0) f.n_qb_part = 0;
+  }
+  cudaError_t e = use_tc ? launch_tc_fwd(f, p->dtype, s) : launch_generic_fwd(f, p->dtype, s);
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "faws: forward launch failed: %s\n", cudaGetErrorString(e));
+    return FAWS_ECUDA;
+  }
+  t_last_backend = use_tc ? FAWS_BACKEND_TCGEN05 : FAWS_BACKEND_GENERIC;
+  return FAWS_OK;
+}
+
+int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, cudaStream_t s) {
+  bool use_tc = false;
+  if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_colsoftmax_supported(c, p->dtype);
+  if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
+  cudaError_t e = use_tc ? launch_tc_colsoftmax(c, p->dtype, s) : launch_generic_colsoftmax(c, p->dtype, s);
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "faws: column-softmax launch failed: %s\n", cudaGetErrorString(e));
+    return FAWS_ECUDA;
+  }
+  return FAWS_OK;
+}
+
+size_t partial_floats(const faws_problem* p, int row_begin, int n_end) {
+  const int first = (row_begin > p->m_begin ? row_begin : p->m_begin) / kGenericBlockM;
+  int nqb = cdiv(p->m_end, kGenericBlockM) - first;
+  if (nqb < 0) nqb = 0;
+  return (size_t)p->B * p->Hq * nqb * (size_t)(cdiv(n_end, 128) * 128);
+}
+
+// Raw column-type sums: forward pass with per-query-block partials + fixed-order reduce.
+int raw_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws, size_t ws_bytes,
+                 void* stream, int schedule, int row_begin, int n_end) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (sum_out == nullptr) return FAWS_EINVAL;
+  const size_t need = align256(partial_floats(p, row_begin, n_end) * 4);
+  if (need > 0 && (ws == nullptr || ws_bytes < need)) return FAWS_EWORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FwdParams f = make_fwd(p);
+  f.schedule = schedule;
+  f.col_partial = static_cast<float*>(ws);
+  f.col_row_begin = row_begin;
+  f.col_n_end = n_end;
+  int bm = 0, bn = 0;
+  st = run_fwd(p, f, s, &bm, &bn);
+  if (st != FAWS_OK) return st;
+  ReducePartialParams r{};
+  r.partial = f.col_partial; r.out = sum_out;
+  r.B = p->B; r.Hq = p->Hq; r.Hk = p->Hk; r.G = p->Hq / p->Hk; r.per_q_head = per_q_head ? 1 : 0;
+  r.n_end = n_end; r.ncols_pad = f.ncols_pad; r.n_qb_part = f.n_qb_part; r.qb_first = f.qb_first;
+  r.block_m = bm; r.block_n = bn;
+  r.causal = f.causal; r.p_seq = f.p_seq; r.N = p->N; r.m_end = p->m_end;
+  if (launch_reduce_partials(r, s) != cudaSuccess) return FAWS_ECUDA;
+  return FAWS_OK;
+}
+
+struct SoftmaxWs {
+  float* L;
+  float* per_head;
+  float* scratch;
+  size_t total;
+};
+
+SoftmaxWs carve_softmax_ws(const faws_problem* p, void* ws, int n_end, int split_for_scratch) {
+  SoftmaxWs w{};
+  size_t off = 0;
+  char* base = static_cast<char*>(ws);
+  const size_t lbytes = align256((size_t)p->B * p->Hq * p->M * 4);
+  const size_t hbytes = align256((size_t)p->B * p->Hq * (size_t)n_end * 4);
+  w.L = reinterpret_cast<float*>(base + off); off += lbytes;
+  w.per_head = reinterpret_cast<float*>(base + off); off += hbytes;
+  if (split_for_scratch > 0 && p->M > split_for_scratch) {
+    w.scratch = reinterpret_cast<float*>(base + off);
+    off += align256((size_t)p->B * p->Hq * (size_t)(p->M - split_for_scratch) * split_for_scratch * 4);
+  }
+  w.total = off;
+  return w;
+}
+
+// Softmax-normalised column-type sums: forward pass (out, L[, score scratch]) then the
+// key-major pass and, unless per-q-head output was asked for, the group sum.
+int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws, size_t ws_bytes,
+                     void* stream, int i_begin, int n_end, int buffered_split, int schedule) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (sum_out == nullptr) return FAWS_EINVAL;
+  SoftmaxWs w = carve_softmax_ws(p, nullptr, n_end, buffered_split);
+  if (ws == nullptr || ws_bytes < w.total) return FAWS_EWORKSPACE;
+  w = carve_softmax_ws(p, ws, n_end, buffered_split);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FwdParams f = make_fwd(p);
+  f.schedule = schedule;
+  if (f.L == nullptr) f.L = w.L;
+  if (w.scratch != nullptr) { f.s_scratch = w.scratch; f.split = buffered_split; }
+  int bm = 0, bn = 0;
+  st = run_fwd(p, f, s, &bm, &bn);
+  if (st != FAWS_OK) return st;
+  const int G = p->Hq / p->Hk;
+  const bool direct = per_q_head || G == 1;
+  ColSoftmaxParams c = make_cs(p, f.L, direct ? sum_out : w.per_head, i_begin, n_end);
+  if (w.scratch != nullptr) { c.s_scratch = w.scratch; c.split = buffered_split; }
+  if (i_begin >= p->m_end) {
+    // no query of the window lies beyond the split: the sums are zero
+    if (cudaMemsetAsync(sum_out, 0, (size_t)p->B * (per_q_head ? p->Hq : p->Hk) * (size_t)n_end * 4, s) != cudaSuccess)
+      return FAWS_ECUDA;
+    return FAWS_OK;
+  }
+  st = run_colsoftmax(p, c, s);
+  if (st != FAWS_OK) return st;
+  if (!direct && launch_group_sum(w.per_head, sum_out, p->B, p->Hk, G, n_end, s) != cudaSuccess)
+    return FAWS_ECUDA;
+  return FAWS_OK;
+}
+
+}  // namespace
+}  // namespace faws
+
+using namespace faws;
+
+extern "C" {
+
+int faws_attention(const faws_problem* p, void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  FwdParams f = make_fwd(p);
+  int bm, bn;
+  return run_fwd(p, f, static_cast<cudaStream_t>(stream), &bm, &bn);
+}
+
+int faws_attention_with_scores(const faws_problem* p, void* scores, int32_t scores_dtype,
+                               uint32_t masked_bits, void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (scores == nullptr) return FAWS_EINVAL;
+  if (scores_dtype != FAWS_SCORES_F32 && scores_dtype != FAWS_SCORES_INPUT) return FAWS_EINVAL;
+  FwdParams f = make_fwd(p);
+  f.scores = scores;
+  f.scores_f32 = scores_dtype == FAWS_SCORES_F32 ? 1 : 0;
+  f.masked_bits = masked_bits;
+  int bm, bn;
+  return run_fwd(p, f, static_cast<cudaStream_t>(stream), &bm, &bn);
+}
+
+int faws_attention_with_row_sum(const faws_problem* p, float* row_sum, void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (row_sum == nullptr) return FAWS_EINVAL;
+  FwdParams f = make_fwd(p);
+  f.row_sum = row_sum;
+  int bm, bn;
+  return run_fwd(p, f, static_cast<cudaStream_t>(stream), &bm, &bn);
+}
+
+int faws_attention_with_col_sum(const faws_problem* p, float* col_sum, int32_t per_q_head,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  if (p == nullptr) return FAWS_EINVAL;
+  return raw_col_sums(p, col_sum, per_q_head, workspace, workspace_bytes, stream,
+                      p->causal ? kReverse : kRoundRobin, 0, p->N);
+}
+
+int faws_attention_with_col_sum_sequential(const faws_problem* p, float* col_sum, int32_t per_q_head,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
+  if (p == nullptr) return FAWS_EINVAL;
+  return raw_col_sums(p, col_sum, per_q_head, workspace, workspace_bytes, stream, kRoundRobin, 0, p->N);
+}
+
+int faws_attention_with_softmax_col_sum(const faws_problem* p, float* col_sum, int32_t per_q_head,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (p == nullptr) return FAWS_EINVAL;
+  return softmax_col_sums(p, col_sum, per_q_head, workspace, workspace_bytes, stream, 0, p->N, 0,
+                          kRoundRobin);
+}
+
+int faws_attention_cross_token_qk_sum(const faws_problem* p, int32_t split, float* sum_out,
+                                      int32_t per_q_head, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
+  if (p == nullptr || split <= 0 || split > p->N) return FAWS_EINVAL;
+  return raw_col_sums(p, sum_out, per_q_head, workspace, workspace_bytes, stream, kForward, split, split);
+}
+
+int faws_attention_cross_token_softmax_sum(const faws_problem* p, int32_t split, float* sum_out,
+                                           int32_t per_q_head, void* workspace,
+                                           size_t workspace_bytes, void* stream) {
+  if (p == nullptr || split <= 0 || split > p->N) return FAWS_EINVAL;
+  return softmax_col_sums(p, sum_out, per_q_head, workspace, workspace_bytes, stream, split, split, 0,
+                          kRoundRobin);
+}
+
+int faws_attention_cross_token_softmax_sum_buffered(const faws_problem* p, int32_t split,
+                                                    float* sum_out, int32_t per_q_head,
+                                                    void* workspace, size_t workspace_bytes,
+                                                    void* stream) {
+  if (p == nullptr || split <= 0 || split > p->N) return FAWS_EINVAL;
+  return softmax_col_sums(p, sum_out, per_q_head, workspace, workspace_bytes, stream, split, split,
+                          split, kForward);
+}
+
+int faws_total_attention(const faws_problem* p, float* total, void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (total == nullptr || p->log_normalizer == nullptr) return FAWS_EINVAL;
+  ColSoftmaxParams c = make_cs(p, p->log_normalizer, total, 0, p->N);
+  return run_colsoftmax(p, c, static_cast<cudaStream_t>(stream));
+}
+
+size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split) {
+  if (validate(p) != FAWS_OK) return 0;
+  switch (op) {
+    case FAWS_OP_COL_SUM:
+    case FAWS_OP_COL_SUM_SEQUENTIAL:
+      return align256(partial_floats(p, 0, p->N) * 4);
+    case FAWS_OP_CROSS_QK_SUM:
+      if (split <= 0 || split > p->N) return 0;
+      return align256(partial_floats(p, split, split) * 4);
+    case FAWS_OP_SOFTMAX_COL_SUM:
+      return carve_softmax_ws(p, nullptr, p->N, 0).total;
+    case FAWS_OP_CROSS_SOFTMAX_SUM:
+      if (split <= 0 || split > p->N) return 0;
+      return carve_softmax_ws(p, nullptr, split, 0).total;
+    case FAWS_OP_CROSS_SOFTMAX_SUM_BUFFERED:
+      if (split <= 0 || split > p->N) return 0;
+      return carve_softmax_ws(p, nullptr, split, split).total;
+    default:
+      return 0;
+  }
+}
+
+int faws_reduce_ranks(const float* parts, int32_t n_ranks, int64_t count, float* out, void* stream) {
+  if (parts == nullptr || out == nullptr || n_ranks <= 0 || count < 0) return FAWS_EINVAL;
+  return launch_reduce_ranks(parts, n_ranks, count, out, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? FAWS_OK
+             : FAWS_ECUDA;
+}
+
+int faws_last_backend(void) { return t_last_backend; }
+int64_t faws_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* faws_strerror(int status) {
+  switch (status) {
+    case FAWS_OK: return "ok";
+    case FAWS_EINVAL: return "invalid argument (shape, pointer, window or split)";
+    case FAWS_EUNSUPPORTED: return "unsupported head dimension or dtype";
+    case FAWS_EWORKSPACE: return "workspace missing or too small";
+    case FAWS_ECUDA: return "CUDA call failed";
+    case FAWS_EBACKEND: return "requested kernel family cannot run this problem";
+    default: return "unknown status";
+  }
+}
+
+int faws_version(void) { return FAWS_VERSION; }
+
+}  // extern "C"

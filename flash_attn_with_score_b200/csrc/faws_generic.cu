@@ -1,0 +1,455 @@
+// CUDA-core kernels of the attention-with-scores family.
+//
+// These cover every shape the operators accept (head dim 16/32/64/128, ragged
+// lengths, M != N, unaligned views).  The tcgen05 kernels in faws_tc.cu take
+// over whenever a problem fits them; these stay as the path for the rest and
+// as the on-device cross-check in the tests.
+//
+// One CTA = 64 query rows of one (batch, query head); key tiles of 64 are
+// streamed through shared memory.  The loop body is the FlashAttention-2
+// forward step (flash.py:432-470) with the score-tile hooks of
+// attention_with_scores.py:141-162 (store), attention_with_row_sum.py:146-156
+// (row reduce) and attention_with_col_sum.py:170-191 (column reduce, written as
+// a per-CTA partial instead of an atomic add).
+#include "faws_internal.cuh"
+
+namespace faws {
+namespace {
+
+constexpr int BM = kGenericBlockM;
+constexpr int BN = kGenericBlockN;
+constexpr int NT = 256;
+constexpr int SLD = BN + 1;
+constexpr float kLog2e = 1.4426950408889634f;
+#define FAWS_NEG_INF (__int_as_float(0xff800000))
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// rows [r0, r0+64) of a (rows, D) matrix -> smem, zero outside [r_lo, r_hi)
+template <typename T>
+__device__ __forceinline__ void load_tile(T* dst, int lds, const T* src, int64_t stride_s, int r0,
+                                          int r_lo, int r_hi, int D, int vec) {
+  if (vec) {
+    const int chunks = D >> 3;
+    for (int idx = threadIdx.x; idx < 64 * chunks; idx += NT) {
+      const int r = idx / chunks, c = idx - r * chunks;
+      const int row = r0 + r;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (row >= r_lo && row < r_hi)
+        val = *reinterpret_cast<const uint4*>(src + (int64_t)row * stride_s + c * 8);
+      *reinterpret_cast<uint4*>(dst + r * lds + c * 8) = val;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < 64 * D; idx += NT) {
+      const int r = idx / D, c = idx - r * D;
+      const int row = r0 + r;
+      T val = from_f<T>(0.f);
+      if (row >= r_lo && row < r_hi) val = src[(int64_t)row * stride_s + c];
+      dst[r * lds + c] = val;
+    }
+  }
+}
+
+// acc[r][c] = sum_d A[(ty*4+r)][d] * Bm[(tx+16c)][d]
+template <typename T>
+__device__ __forceinline__ void tile_dot(const T* A, const T* Bm, int lds, int D, int ty, int tx,
+                                         float (&acc)[4][4]) {
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+  for (int d = 0; d < D; d += 2) {
+    float ax[4], ay[4], bx[4], by[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      ax[r] = to_f(A[(ty * 4 + r) * lds + d]);
+      ay[r] = to_f(A[(ty * 4 + r) * lds + d + 1]);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      bx[c] = to_f(Bm[(tx + 16 * c) * lds + d]);
+      by[c] = to_f(Bm[(tx + 16 * c) * lds + d + 1]);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[r][c] = fmaf(ax[r], bx[c], fmaf(ay[r], by[c], acc[r][c]));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT) generic_fwd_kernel(FwdParams p, int vec) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = p.D, lds = D + 8;
+  T* Qs = reinterpret_cast<T*>(smem_raw);
+  T* Ks = Qs + BM * lds;
+  T* Vs = Ks + BN * lds;
+  float* Ss = reinterpret_cast<float*>(Vs + BN * lds);
+  float* m_s = Ss + BM * SLD;
+  float* l_s = m_s + BM;
+  float* a_s = l_s + BM;
+
+  const int tid = threadIdx.x;
+  const int qb_abs = p.m_begin / BM + blockIdx.x;
+  const int m0 = qb_abs * BM;
+  const int h = blockIdx.y, b = blockIdx.z, hk = h / p.G;
+  const int ty = tid >> 4, tx = tid & 15;
+
+  const T* qp = reinterpret_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+  const T* kp = reinterpret_cast<const T*>(p.k) + b * p.k_sb + hk * p.k_sh;
+  const T* vp = reinterpret_cast<const T*>(p.v) + b * p.v_sb + hk * p.v_sh;
+  T* op = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh;
+  const int64_t bh = (int64_t)b * p.Hq + h;
+
+  load_tile(Qs, lds, qp, p.q_ss, m0, p.m_begin, p.m_end, D, vec);
+  if (tid < BM) {
+    m_s[tid] = FAWS_NEG_INF;
+    l_s[tid] = 0.f;
+    a_s[tid] = 1.f;
+  }
+  float o[4][8];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) o[r][c] = 0.f;
+  float rs_acc = 0.f;
+  const int ncd = D >> 4;  // output columns per thread in the PV step
+
+  int hi = p.N;
+  if (p.causal) {
+    const int last = min(m0 + BM, p.m_end);
+    hi = max(0, min(p.N, p.p_seq + last));
+  }
+  const int nt = (hi + BN - 1) / BN;
+  const float masked_f = __uint_as_float(p.masked_bits);
+  const bool part_on = p.col_partial != nullptr && qb_abs >= p.qb_first &&
+                       (m0 + BM) > p.col_row_begin;
+
+  for (int it = 0; it < nt; ++it) {
+    int t = it;
+    if (p.schedule == kReverse) t = nt - 1 - it;
+    else if (p.schedule == kRoundRobin) t = (qb_abs + it) % nt;
+    const int n0 = t * BN;
+    __syncthreads();
+    load_tile(Ks, lds, kp, p.k_ss, n0, 0, p.N, D, vec);
+    load_tile(Vs, lds, vp, p.v_ss, n0, 0, p.N, D, vec);
+    __syncthreads();
+
+    float acc[4][4];
+    tile_dot(Qs, Ks, lds, D, ty, tx, acc);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = m0 + ty * 4 + r;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = n0 + tx + 16 * c;
+        const float s = acc[r][c] * p.sm_scale;
+        const bool inb = i >= p.m_begin && i < p.m_end && j < p.N;
+        const bool vis = inb && (!p.causal || j <= i + p.p_seq);
+        if (p.scores != nullptr && inb) {
+          const int64_t off = (bh * p.M + i) * (int64_t)p.N + j;
+          const float val = vis ? s : masked_f;
+          if (p.scores_f32) reinterpret_cast<float*>(p.scores)[off] = val;
+          else reinterpret_cast<T*>(p.scores)[off] = from_f<T>(val);
+        }
+        if (p.s_scratch != nullptr && inb && i >= p.split && j < p.split)
+          p.s_scratch[(bh * (p.M - p.split) + (i - p.split)) * (int64_t)p.split + j] =
+              vis ? s : FAWS_NEG_INF;
+        Ss[(ty * 4 + r) * SLD + tx + 16 * c] = vis ? s : FAWS_NEG_INF;
+      }
+    }
+    __syncthreads();
+
+    if (p.col_partial != nullptr) {  // uniform branch
+      if (part_on && tid < BN && n0 + tid < p.ncols_pad) {
+        float sum = 0.f;
+        for (int r = 0; r < BM; ++r) {
+          const float val = Ss[r * SLD + tid];
+          if (m0 + r >= p.col_row_begin && val != FAWS_NEG_INF) sum += val;
+        }
+        p.col_partial[(bh * p.n_qb_part + (qb_abs - p.qb_first)) * (int64_t)p.ncols_pad + n0 + tid] = sum;
+      }
+      __syncthreads();
+    }
+
+    {  // online softmax, 4 threads per row
+      const int row = tid >> 2, qd = tid & 3;
+      float mx = FAWS_NEG_INF;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) mx = fmaxf(mx, Ss[row * SLD + qd + 4 * c]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_old = m_s[row];
+      const float l_old = l_s[row];
+      const float m_new = fmaxf(m_old, mx);
+      const float alpha = (m_new == FAWS_NEG_INF) ? 1.f : exp2f((m_old - m_new) * kLog2e);
+      float psum = 0.f, rsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const float s = Ss[row * SLD + qd + 4 * c];
+        const bool hid = (s == FAWS_NEG_INF);
+        const float pr = hid ? 0.f : exp2f((s - m_new) * kLog2e);
+        rsum += hid ? 0.f : s;
+        psum += pr;
+        Ss[row * SLD + qd + 4 * c] = to_f(from_f<T>(pr));
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      rs_acc += rsum;
+      __syncwarp();
+      if (qd == 0) {
+        m_s[row] = m_new;
+        l_s[row] = l_old * alpha + psum;
+        a_s[row] = alpha;
+      }
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float a = a_s[ty * 4 + r];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) o[r][c] *= a;
+    }
+    for (int n = 0; n < BN; ++n) {
+      float pv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) pv[r] = Ss[(ty * 4 + r) * SLD + n];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < ncd) {
+          const float vv = to_f(Vs[n * lds + tx + 16 * c]);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) o[r][c] = fmaf(pv[r], vv, o[r][c]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = m0 + ty * 4 + r;
+    if (i >= p.m_begin && i < p.m_end) {
+      const float l = l_s[ty * 4 + r];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c < ncd) op[(int64_t)i * p.o_ss + tx + 16 * c] = from_f<T>(o[r][c] * inv);
+    }
+  }
+  if (p.L != nullptr && tid < BM) {
+    const int i = m0 + tid;
+    if (i >= p.m_begin && i < p.m_end) {
+      const float l = l_s[tid];
+      p.L[bh * p.M + i] = l > 0.f ? m_s[tid] + logf(l) : FAWS_NEG_INF;
+    }
+  }
+  if (p.row_sum != nullptr) {
+    rs_acc += __shfl_xor_sync(0xffffffffu, rs_acc, 1);
+    rs_acc += __shfl_xor_sync(0xffffffffu, rs_acc, 2);
+    const int i = m0 + (tid >> 2);
+    if ((tid & 3) == 0 && i >= p.m_begin && i < p.m_end) p.row_sum[bh * p.M + i] = rs_acc;
+  }
+  if (p.scores != nullptr) {  // key tiles the causal loop never visits: all hidden
+    const int c_begin = nt * BN;
+    const int width = p.N - c_begin;
+    if (width > 0) {
+      for (int idx = tid; idx < BM * width; idx += NT) {
+        const int r = idx / width, j = c_begin + (idx - r * width);
+        const int i = m0 + r;
+        if (i >= p.m_begin && i < p.m_end) {
+          const int64_t off = (bh * p.M + i) * (int64_t)p.N + j;
+          if (p.scores_f32) reinterpret_cast<float*>(p.scores)[off] = masked_f;
+          else reinterpret_cast<T*>(p.scores)[off] = from_f<T>(masked_f);
+        }
+      }
+    }
+  }
+}
+
+// Key-major softmax column sums (the structure of total.py:50-142): a CTA owns
+// 64 keys and walks the query tiles; thread c < 64 accumulates column c in a
+// register in a fixed order, so there are no atomics and no partials.
+template <typename T>
+__global__ void __launch_bounds__(NT) generic_colsoftmax_kernel(ColSoftmaxParams p, int vec) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = p.D, lds = D + 8;
+  T* Ks = reinterpret_cast<T*>(smem_raw);
+  T* Qs = Ks + BN * lds;
+  float* Ss = reinterpret_cast<float*>(Qs + BM * lds);
+  float* Ls = Ss + BM * SLD;
+
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * BN;
+  const int h = blockIdx.y, b = blockIdx.z, hk = h / p.G;
+  const int ty = tid >> 4, tx = tid & 15;
+  const T* qp = reinterpret_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+  const T* kp = reinterpret_cast<const T*>(p.k) + b * p.k_sb + hk * p.k_sh;
+  const int64_t bh = (int64_t)b * p.Hq + h;
+  const bool from_scratch = p.s_scratch != nullptr;
+
+  if (!from_scratch) load_tile(Ks, lds, kp, p.k_ss, n0, 0, min(p.N, p.n_end), D, vec);
+  int i_lo = max(p.i_begin, p.m_begin);
+  int i_start = i_lo;
+  if (p.causal) i_start = max(i_start, n0 - p.p_seq);
+  float colacc = 0.f;
+  for (int m0 = (i_start / BM) * BM; m0 < p.m_end; m0 += BM) {
+    __syncthreads();
+    if (!from_scratch) load_tile(Qs, lds, qp, p.q_ss, m0, i_lo, p.m_end, D, vec);
+    if (tid < BM) {
+      const int i = m0 + tid;
+      Ls[tid] = (i >= i_lo && i < p.m_end) ? p.L[bh * p.M + i] : FAWS_NEG_INF;
+    }
+    __syncthreads();
+    float acc[4][4];
+    if (!from_scratch) tile_dot(Qs, Ks, lds, D, ty, tx, acc);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int i = m0 + ty * 4 + r;
+      const float Li = Ls[ty * 4 + r];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int j = n0 + tx + 16 * c;
+        const bool vis = i >= i_lo && i < p.m_end && j < p.n_end && j < p.N &&
+                         (!p.causal || j <= i + p.p_seq) && Li != FAWS_NEG_INF;
+        float s = 0.f;
+        if (vis) {
+          s = from_scratch
+                  ? p.s_scratch[(bh * (p.M - p.split) + (i - p.split)) * (int64_t)p.split + j]
+                  : acc[r][c] * p.sm_scale;
+        }
+        Ss[(ty * 4 + r) * SLD + tx + 16 * c] = vis ? exp2f((s - Li) * kLog2e) : 0.f;
+      }
+    }
+    __syncthreads();
+    if (tid < BN) {
+      for (int r = 0; r < BM; ++r) colacc += Ss[r * SLD + tid];
+    }
+  }
+  if (tid < BN && n0 + tid < p.n_end) p.out[bh * p.n_end + n0 + tid] = colacc;
+}
+
+// out[b,ho,j] = sum over the group's heads (or the single head) and over the
+// query blocks that visited column j, in a fixed order.
+__global__ void reduce_partials_kernel(ReducePartialParams p) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= p.n_end) return;
+  const int ho = blockIdx.y, b = blockIdx.z;
+  const int h0 = p.per_q_head ? ho : ho * p.G;
+  const int nh = p.per_q_head ? 1 : p.G;
+  const int Hout = p.per_q_head ? p.Hq : p.Hk;
+  const int tile_start = (j / p.block_n) * p.block_n;
+  float sum = 0.f;
+  for (int g = 0; g < nh; ++g) {
+    const float* base = p.partial + ((int64_t)(b * p.Hq + h0 + g) * p.n_qb_part) * p.ncols_pad;
+    for (int qb = 0; qb < p.n_qb_part; ++qb) {
+      if (p.causal) {
+        const int last = min((p.qb_first + qb + 1) * p.block_m, p.m_end);
+        const int hi = min(p.N, p.p_seq + last);
+        if (tile_start >= hi) continue;  // the forward kernel never visited this key tile
+      }
+      sum += base[(int64_t)qb * p.ncols_pad + j];
+    }
+  }
+  p.out[((int64_t)b * Hout + ho) * p.n_end + j] = sum;
+}
+
+__global__ void group_sum_kernel(const float* in, float* out, int Hk, int G, int len) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= len) return;
+  const int hk = blockIdx.y, b = blockIdx.z;
+  float sum = 0.f;
+  for (int g = 0; g < G; ++g) sum += in[((int64_t)(b * Hk + hk) * G + g) * len + j];
+  out[((int64_t)b * Hk + hk) * len + j] = sum;
+}
+
+__global__ void reduce_ranks_kernel(const float* parts, int n_ranks, int64_t count, float* out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  float sum = 0.f;
+  for (int r = 0; r < n_ranks; ++r) sum += parts[(int64_t)r * count + i];
+  out[i] = sum;
+}
+
+size_t fwd_smem(int D) { return (size_t)(3 * 64 * (D + 8)) * 2 + (size_t)(BM * SLD + 3 * BM) * 4; }
+size_t cs_smem(int D) { return (size_t)(2 * 64 * (D + 8)) * 2 + (size_t)(BM * SLD + BM) * 4; }
+
+template <typename K>
+cudaError_t set_smem(K kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+bool aligned16(const void* ptr, int64_t a, int64_t b, int64_t c) {
+  return (reinterpret_cast<uintptr_t>(ptr) % 16 == 0) && a % 8 == 0 && b % 8 == 0 && c % 8 == 0;
+}
+
+}  // namespace
+
+cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
+  const int vec = aligned16(p.q, p.q_sb, p.q_sh, p.q_ss) && aligned16(p.k, p.k_sb, p.k_sh, p.k_ss) &&
+                  aligned16(p.v, p.v_sb, p.v_sh, p.v_ss);
+  const int nqb = (p.m_end + BM - 1) / BM - p.m_begin / BM;
+  if (nqb <= 0) return cudaSuccess;
+  dim3 grid(nqb, p.Hq, p.B);
+  const size_t smem = fwd_smem(p.D);
+  cudaError_t e;
+  if (dtype == FAWS_FP16) {
+    if ((e = set_smem(generic_fwd_kernel<__half>, smem)) != cudaSuccess) return e;
+    generic_fwd_kernel<__half><<<grid, NT, smem, s>>>(p, vec);
+  } else {
+    if ((e = set_smem(generic_fwd_kernel<__nv_bfloat16>, smem)) != cudaSuccess) return e;
+    generic_fwd_kernel<__nv_bfloat16><<<grid, NT, smem, s>>>(p, vec);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s) {
+  const int vec = aligned16(p.q, p.q_sb, p.q_sh, p.q_ss) && aligned16(p.k, p.k_sb, p.k_sh, p.k_ss);
+  if (p.n_end <= 0) return cudaSuccess;
+  dim3 grid((p.n_end + BN - 1) / BN, p.Hq, p.B);
+  const size_t smem = cs_smem(p.D);
+  cudaError_t e;
+  if (dtype == FAWS_FP16) {
+    if ((e = set_smem(generic_colsoftmax_kernel<__half>, smem)) != cudaSuccess) return e;
+    generic_colsoftmax_kernel<__half><<<grid, NT, smem, s>>>(p, vec);
+  } else {
+    if ((e = set_smem(generic_colsoftmax_kernel<__nv_bfloat16>, smem)) != cudaSuccess) return e;
+    generic_colsoftmax_kernel<__nv_bfloat16><<<grid, NT, smem, s>>>(p, vec);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_partials(const ReducePartialParams& p, cudaStream_t s) {
+  if (p.n_end <= 0) return cudaSuccess;
+  dim3 grid((p.n_end + 255) / 256, p.per_q_head ? p.Hq : p.Hk, p.B);
+  reduce_partials_kernel<<<grid, 256, 0, s>>>(p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, int len,
+                             cudaStream_t s) {
+  if (len <= 0) return cudaSuccess;
+  dim3 grid((len + 255) / 256, Hk, B);
+  group_sum_kernel<<<grid, 256, 0, s>>>(in, out, Hk, G, len);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_ranks(const float* parts, int n_ranks, int64_t count, float* out,
+                                cudaStream_t s) {
+  if (count <= 0) return cudaSuccess;
+  reduce_ranks_kernel<<<(unsigned)((count + 255) / 256), 256, 0, s>>>(parts, n_ranks, count, out);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace faws

@@ -1,0 +1,96 @@
+// Shared between the ABI layer and the kernel translation units.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "faws.h"
+
+namespace faws {
+
+// Key-tile visiting orders (attention_with_col_sum.py:119-137 reverse,
+// attention_with_col_sum_sequential.py:116-122 round-robin, flash.py:432 forward).
+enum Schedule : int { kForward = 0, kReverse = 1, kRoundRobin = 2 };
+
+// Everything a forward kernel needs.  Plain data, passed by value.
+struct FwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  int64_t v_sb, v_sh, v_ss;
+  int64_t o_sb, o_sh, o_ss;
+  float* L;  // (B,Hq,M) or null
+  int B, Hq, Hk, G, M, N, D;
+  int p_seq;             // N - M: key j visible to query i iff j <= i + p_seq
+  int m_begin, m_end;    // query-row window
+  int causal;
+  float sm_scale;
+  int schedule;
+  // --- score-tile hooks (null pointer = hook off) ---
+  void* scores;          // (B,Hq,M,N) contiguous
+  int scores_f32;        // 1: fp32, 0: input dtype
+  uint32_t masked_bits;  // fp32 bit pattern written at hidden entries
+  float* row_sum;        // (B,Hq,M)
+  float* col_partial;    // (B,Hq,n_qb_part,ncols_pad): per-query-block column sums
+  int col_row_begin;     // only queries i >= this contribute (0, or split)
+  int col_n_end;         // only keys j < this are summed (N, or split)
+  int ncols_pad;         // col_n_end rounded up to the key-tile width
+  int qb_first;          // first query block (of width block_m) that owns a partial row
+  int n_qb_part;         // partial rows per (b,h)
+  float* s_scratch;      // buffered variant: (B,Hq,M-split,split) scaled scores
+  int split;
+};
+
+// Key-major softmax column-sum pass: out[b,h,j] = sum_{i>=i_begin, visible} exp(s_ij - L_i).
+struct ColSoftmaxParams {
+  const void* q;
+  const void* k;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  const float* L;        // (B,Hq,M)
+  float* out;            // (B,Hq,n_end) per query head
+  int B, Hq, Hk, G, M, N, D;
+  int p_seq, m_begin, m_end, causal;
+  float sm_scale;
+  int i_begin;           // queries i >= i_begin
+  int n_end;             // keys j < n_end
+  const float* s_scratch;  // if non-null read scaled scores (B,Hq,M-split,split) instead of q.k
+  int split;
+};
+
+struct ReducePartialParams {
+  const float* partial;  // (B,Hq,n_qb_part,ncols_pad)
+  float* out;            // (B,Hout,n_end)
+  int B, Hq, Hk, G, per_q_head;
+  int n_end, ncols_pad, n_qb_part, qb_first;
+  int block_m, block_n;  // tile sizes the forward kernel used
+  int causal, p_seq, N, m_end;
+};
+
+// Launchers (each returns a cudaError_t from the launch).
+cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_reduce_partials(const ReducePartialParams& p, cudaStream_t s);
+cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, int len,
+                             cudaStream_t s);
+cudaError_t launch_reduce_ranks(const float* parts, int n_ranks, int64_t count, float* out,
+                                cudaStream_t s);
+
+// tcgen05 family.  tc_supported() is a pure host-side check.
+bool tc_fwd_supported(const FwdParams& p, int dtype);
+cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s);
+bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype);
+cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
+
+constexpr int kGenericBlockM = 64;
+constexpr int kGenericBlockN = 64;
+constexpr int kTcBlockM = 128;
+constexpr int kTcBlockN = 128;
+
+void count_launch(int n = 1);
+
+}  // namespace faws
