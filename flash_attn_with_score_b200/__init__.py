@@ -11,6 +11,7 @@ from .api import (  # noqa: F401
     attention_with_row_sum,
     attention_with_scores,
     attention_with_softmax_col_sum,
+    device_status,
     last_backend,
     launch_count,
     total_attention,

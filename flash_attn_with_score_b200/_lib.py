@@ -23,7 +23,7 @@ EXPORTS = [
     "faws_attention_with_col_sum", "faws_attention_with_col_sum_sequential",
     "faws_attention_with_softmax_col_sum", "faws_attention_cross_token_qk_sum",
     "faws_attention_cross_token_softmax_sum", "faws_attention_cross_token_softmax_sum_buffered",
-    "faws_total_attention", "faws_workspace_bytes", "faws_reduce_ranks", "faws_last_backend",
+    "faws_total_attention", "faws_workspace_bytes", "faws_reduce_ranks", "faws_device_status", "faws_last_backend",
     "faws_launch_count", "faws_strerror", "faws_version",
 ]
 
@@ -71,6 +71,7 @@ def load():
         "faws_total_attention": (i32, [PP, vp, vp]),
         "faws_workspace_bytes": (sz, [i32, PP, i32]),
         "faws_reduce_ranks": (i32, [vp, i32, C.c_int64, vp, vp]),
+        "faws_device_status": (i32, [i32]),
         "faws_last_backend": (i32, []),
         "faws_launch_count": (C.c_int64, []),
         "faws_strerror": (C.c_char_p, [i32]),

@@ -260,3 +260,8 @@ def last_backend() -> str:
 
 def launch_count() -> int:
     return int(_lib.load().faws_launch_count())
+
+
+def device_status(reset: bool = True) -> int:
+    """Synchronise and read the give-up flag of the tcgen05 kernels' bounded waits (0 = clean)."""
+    return int(_lib.load().faws_device_status(1 if reset else 0))

@@ -309,6 +309,8 @@ int faws_reduce_ranks(const float* parts, int32_t n_ranks, int64_t count, float*
              : FAWS_ECUDA;
 }
 
+int faws_device_status(int32_t reset) { return tc_read_status(reset); }
+
 int faws_last_backend(void) { return t_last_backend; }
 int64_t faws_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -86,6 +86,8 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype);
 cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
 
+int tc_read_status(int reset);  // synchronising read of the device status word
+
 constexpr int kGenericBlockM = 64;
 constexpr int kGenericBlockN = 64;
 constexpr int kTcBlockM = 128;

@@ -1,8 +1,610 @@
-// placeholder: tcgen05 kernels
+// tcgen05 / TMEM / TMA kernels (sm_100a) of the attention-with-scores family.
+//
+// Forward kernel: one CTA = 128 query rows of one (batch, query head), key tiles
+// of 128.  Warp roles:
+//   warp 0      TMA producer: Q once, then K and V tiles through 2-stage rings
+//   warp 1      allocates TMEM; one lane issues the tcgen05 MMAs
+//               S = Q.K^T (fp32, TMEM, double buffered) and O += P.V (fp32, TMEM)
+//   warps 2..5  softmax: thread r owns query row r (TMEM lane r).  It reads S twice
+//               (pass 1: running max + score-tile hooks, pass 2: exp2 and P), rescales
+//               O in TMEM only when the running max moved by more than 2^8, and writes
+//               P as 16-bit into a 128B-swizzled smem tile for the second MMA.
+// Score-tile hooks (what attention_with_scores.py:141-162, attention_with_row_sum.py:146-156,
+// attention_with_col_sum.py:170-191 add to the FlashAttention loop):
+//   scores      fp32 tile staged per warp (32x32, swizzled) and written with TMA stores;
+//               key tiles the causal loop never visits are filled from one constant tile
+//   row sum     per-thread running sum
+//   column sum  per-warp transpose-reduce with shuffles, 4 warps combined through smem,
+//               one partial row per query block (summed later in fixed order)
+//   scratch     the cross region's scores (buffered cross-token variant) via TMA stores
+//
+// Every mbarrier wait is bounded (2 s); on give-up the CTA raises a flag in *status,
+// lets in-flight copies drain, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <cstdio>
+#include <mutex>
+#include <type_traits>
+
 #include "faws_internal.cuh"
+#include "faws_tc_ptx.cuh"
+
 namespace faws {
-bool tc_fwd_supported(const FwdParams&, int) { return false; }
-cudaError_t launch_tc_fwd(const FwdParams&, int, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+using namespace ptx;
+
+constexpr int BM = kTcBlockM;
+constexpr int BN = kTcBlockN;
+constexpr int NTHREADS = 192;
+constexpr int KV_STAGES = 2;
+constexpr int TMEM_COLS = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#define FAWS_NEG_INF (__int_as_float(0xff800000))
+
+struct TcMaps {
+  CUtensorMap q, k, v, st;  // st: scores (or score-scratch) store map
+};
+
+template <int D>
+struct Smem {
+  static constexpr int kTile = 128 * D * 2;  // one Q / K / V tile
+  static constexpr int kSub = 128 * 128;     // one 64-element-wide sub-tile: 128 rows x 128 B
+  static constexpr int q_off = 0;
+  static constexpr int k_off = q_off + kTile;
+  static constexpr int v_off = k_off + KV_STAGES * kTile;
+  static constexpr int p_off = v_off + KV_STAGES * kTile;  // P: 128 x 128 x 16 bit
+  static constexpr int stage_off = p_off + 2 * kSub;       // 4 warps x 2 x 4 KB
+  static constexpr int bar_off = stage_off + 4 * 2 * 4096;
+  static constexpr int total = bar_off + 256;
+  static constexpr int alloc = total + 1024;  // slack to align the base to 1024 B
+};
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+  uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2];
+  uint64_t p_ready;
+  uint64_t pv_done;
+  uint64_t col_ready;  // column-sum hook: the 4 softmax warps' partial rows are in smem
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// In-warp transpose-reduce: on entry lane L holds v[0..31] (its row, 32 columns); on exit
+// v[0] of lane c is the sum over the 32 lanes of their v[c].  31 shuffles.
+__device__ __forceinline__ void warp_column_sums(float (&v)[32], int lane) {
+#pragma unroll
+  for (int step = 16; step >= 1; step >>= 1) {
+    const bool upper = (lane & step) != 0;
+#pragma unroll
+    for (int x = 0; x < step; ++x) {
+      const float send = upper ? v[x] : v[x + step];
+      const float keep = upper ? v[x + step] : v[x];
+      v[x] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+    }
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __restrict__ status) {
+  using L = Smem<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  Bars* bars = reinterpret_cast<Bars*>(smem + L::bar_off);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = gridDim.x;
+  const int qb_rel = nqb - 1 - (int)blockIdx.x;  // heaviest (last) causal blocks first
+  const int qb_abs = p.m_begin / BM + qb_rel;
+  const int m0 = qb_abs * BM;
+  const int h = blockIdx.y, b = blockIdx.z, hk = h / p.G;
+  const int bh = b * p.Hq + h;
+
+  int hi = p.N;
+  if (p.causal) hi = max(0, min(p.N, p.p_seq + min(m0 + BM, p.m_end)));
+  const int nt = (hi + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
+    mbar_init(&bars->p_ready, 128);
+    mbar_init(&bars->pv_done, 1);
+    mbar_init(&bars->col_ready, 128);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&maps.q);
+    prefetch_tmap(&maps.k);
+    prefetch_tmap(&maps.v);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  auto tile_of = [&](int it) -> int {
+    if (p.schedule == kReverse) return nt - 1 - it;
+    if (p.schedule == kRoundRobin) return (qb_abs + it) % nt;
+    return it;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&bars->q_full, L::kTile);
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_4d(smem + L::q_off + c * L::kSub, &maps.q, &bars->q_full, c * 64, m0 - p.m_begin, h, b);
+      for (int it = 0; it < nt; ++it) {
+        const int s = it % KV_STAGES, u = it / KV_STAGES;
+        const int n0 = tile_of(it) * BN;
+        if (!mbar_wait(&bars->k_empty[s], (u & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->k_full[s], L::kTile);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::k_off + s * L::kTile + c * L::kSub, &maps.k, &bars->k_full[s], c * 64, n0, hk, b);
+        if (!mbar_wait(&bars->v_empty[s], (u & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->v_full[s], L::kTile);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::v_off + s * L::kTile + c * L::kSub, &maps.v, &bars->v_full[s], c * 64, n0, hk, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && nt > 0) {
+      constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
+      constexpr uint32_t idesc_qk = make_idesc_f16(128, BN, kFmt, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, 0, 1);
+      const uint32_t q_addr = smem_u32(smem + L::q_off);
+      const uint32_t p_addr = smem_u32(smem + L::p_off);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      auto issue_qk = [&](int t) -> bool {
+        const int s = t % KV_STAGES, u = t / KV_STAGES;
+        if (!mbar_wait(&bars->k_full[s], u & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + L::k_off + s * L::kTile);
+        const uint32_t d_tmem = tmem_base + (uint32_t)((t & 1) * BN);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
+          mma_ss(d_tmem, make_desc_sw128(q_addr + off, 16, 1024), make_desc_sw128(k_addr + off, 16, 1024),
+                 idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&bars->k_empty[s]);
+        mma_commit(&bars->s_full[t & 1]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int it = 0; ok && it < nt; ++it) {
+        if (it + 1 < nt && !issue_qk(it + 1)) break;
+        const int s = it % KV_STAGES, u = it / KV_STAGES;
+        if (!mbar_wait(&bars->p_ready, it & 1, abort_flag)) break;
+        if (!mbar_wait(&bars->v_full[s], u & 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + L::v_off + s * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t a_off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
+          mma_ss(tmem_o, make_desc_sw128(p_addr + a_off, 16, 1024),
+                 make_desc_sw128(v_addr + (uint32_t)(kk * 16 * 128), L::kSub, 1024), idesc_pv,
+                 (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(&bars->v_empty[s]);
+        mma_commit(&bars->pv_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps
+    const int lg = warp & 3;  // TMEM lane group this warp may touch
+    const int row = lg * 32 + lane;
+    const int i = m0 + row;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
+    const bool row_ok = i >= p.m_begin && i < p.m_end;
+    const float scale = p.sm_scale;
+    const float scale_log2 = p.sm_scale * kLog2e;
+    unsigned char* stage = smem + L::stage_off + (warp - 2) * 8192;
+    float* colbuf = reinterpret_cast<float*>(smem + L::stage_off);  // [2][4][128], col hook only
+    const bool store_scores = p.scores != nullptr;
+    const bool store_scratch = p.s_scratch != nullptr;
+    const bool part_on = p.col_partial != nullptr && qb_abs >= p.qb_first;
+    const float masked_f = __uint_as_float(p.masked_bits);
+    unsigned char* p_smem = smem + L::p_off;
+    int n_stage = 0;  // staging-buffer uses so far (this warp)
+
+    float m_run = FAWS_NEG_INF, l_run = 0.f, rs = 0.f;
+    bool alive = true;
+
+    for (int it = 0; it < nt; ++it) {
+      const int n0 = tile_of(it) * BN;
+      const int buf = it & 1;
+      if (!mbar_wait(&bars->s_full[buf], (it >> 1) & 1, abort_flag)) { alive = false; break; }
+      tc_fence_after();
+      const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= m0 + p.p_seq));
+      const uint32_t t_s = t_lane + (uint32_t)(buf * BN);
+
+      // ---- pass 1: running max and the score-tile hooks
+      float mx = FAWS_NEG_INF;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_s + c * 32, r);
+        tmem_wait_ld();
+        const int jb = n0 + c * 32;
+        uint32_t vis_mask = 0xffffffffu;
+        if (!full_vis) {
+          vis_mask = 0;
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            const int j = jb + x;
+            if (j < p.N && (!p.causal || j <= i + p.p_seq)) vis_mask |= (1u << x);
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const float raw = __uint_as_float(r[x]);
+          mx = fmaxf(mx, ((vis_mask >> x) & 1u) ? raw * scale_log2 : FAWS_NEG_INF);
+        }
+        if (p.row_sum != nullptr) {
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            rs += ((vis_mask >> x) & 1u) ? __uint_as_float(r[x]) * scale : 0.f;
+        }
+        const bool do_scores = store_scores;
+        const bool do_scratch = store_scratch && (m0 + lg * 32 >= p.split) && (jb < p.split);
+        if (do_scores || do_scratch) {
+          unsigned char* sb = stage + (n_stage & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) {
+            float4 val;
+            float* vp = reinterpret_cast<float*>(&val);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int x = cc * 4 + e;
+              const float sc = __uint_as_float(r[x]) * scale;
+              vp[e] = (do_scratch || ((vis_mask >> x) & 1u)) ? sc : masked_f;
+            }
+            *reinterpret_cast<float4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = val;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int r0 = m0 + lg * 32 - p.m_begin;
+            if (do_scores) tma_store_3d(&maps.st, sb, jb, r0, bh);
+            else tma_store_3d(&maps.st, sb, jb, m0 + lg * 32 - p.split, bh);
+            tma_store_commit();
+          }
+          ++n_stage;
+        }
+        if (p.col_partial != nullptr) {
+          float cv[32];
+          const bool contrib = row_ok && i >= p.col_row_begin;
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            cv[x] = (contrib && ((vis_mask >> x) & 1u)) ? __uint_as_float(r[x]) * scale : 0.f;
+          warp_column_sums(cv, lane);
+          colbuf[(buf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
+        }
+      }
+      if (p.col_partial != nullptr) {
+        mbar_arrive(&bars->col_ready);
+        if (!mbar_wait(&bars->col_ready, it & 1, abort_flag)) { alive = false; break; }
+        if (part_on && n0 + row < p.ncols_pad) {
+          const float* cb = colbuf + buf * 512;
+          // fixed order: the warps that own rows 0-31, 32-63, 64-95, 96-127
+          const float sum = ((cb[row] + cb[128 + row]) + cb[256 + row]) + cb[384 + row];
+          p.col_partial[((int64_t)bh * p.n_qb_part + (qb_abs - p.qb_first)) * (int64_t)p.ncols_pad + n0 + row] = sum;
+        }
+      }
+
+      // ---- running max, lazy rescale of O
+      const float m_new = fmaxf(m_run, mx);
+      const bool need = m_new > m_run + kRescaleThreshold;
+      float alpha = 1.f;
+      if (need) {
+        alpha = exp2f(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+      }
+      if (it > 0) {
+        if (!mbar_wait(&bars->pv_done, (it - 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
+            tmem_st32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, r);
+          }
+          tmem_wait_st();
+        }
+      }
+
+      // ---- pass 2: P = exp2(t - m), row sum of P, P -> smem (K-major, 128B swizzle)
+      const float m_use = (m_run == FAWS_NEG_INF) ? 0.f : m_run;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_s + c * 32, r);
+        tmem_wait_ld();
+        const int jb = n0 + c * 32;
+        float pr[32];
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int j = jb + x;
+          const bool vis = full_vis || (j < p.N && (!p.causal || j <= i + p.p_seq));
+          const float t = vis ? __uint_as_float(r[x]) * scale_log2 - m_use : FAWS_NEG_INF;
+          pr[x] = exp2f(t);
+          l_run += pr[x];
+        }
+        unsigned char* prow = p_smem + (c >> 1) * L::kSub + row * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack2<T>(pr[g * 8 + 0], pr[g * 8 + 1]);
+          w.y = pack2<T>(pr[g * 8 + 2], pr[g * 8 + 3]);
+          w.z = pack2<T>(pr[g * 8 + 4], pr[g * 8 + 5]);
+          w.w = pack2<T>(pr[g * 8 + 6], pr[g * 8 + 7]);
+          const int cc = (c & 1) * 4 + g;
+          *reinterpret_cast<uint4*>(prow + ((cc ^ (row & 7)) << 4)) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready);
+    }
+
+    // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
+    if (alive && nt > 0) {
+      if (!mbar_wait(&bars->pv_done, (nt - 1) & 1, abort_flag)) alive = false;
+      tc_fence_after();
+    }
+    if (alive) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh + (int64_t)i * p.o_ss;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        if (nt > 0) {
+          tmem_ld32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; ++x) r[x] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+            w.y = pack2<T>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+            w.z = pack2<T>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+            w.w = pack2<T>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+          }
+        }
+      }
+      if (row_ok) {
+        if (p.L != nullptr)
+          p.L[(int64_t)bh * p.M + i] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : FAWS_NEG_INF;
+        if (p.row_sum != nullptr) p.row_sum[(int64_t)bh * p.M + i] = rs;
+      }
+      if (store_scores && nt * BN < p.N) {
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<float4*>(stage + lane * 128 + (cc << 4)) = fill;
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int r0 = m0 + lg * 32 - p.m_begin;
+          for (int j0 = nt * BN; j0 < p.N; j0 += 32) tma_store_3d(&maps.st, stage, j0, r0, bh);
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  // ------------------------------------------------------------ common exit
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
+    // give copies that are still in flight time to land before the smem goes away
+    for (int w = 0; w < 50; ++w) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// (rows, 64 x 16-bit) boxes out of a (B, H, S, D) view
+bool make_map_bhsd(CUtensorMap* m, const void* base, int D, int rows, int H, int B, int64_t ss, int64_t sh,
+                   int64_t sb, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+  const cuuint64_t row_bytes = (cuuint64_t)ss * 2;
+  cuuint64_t strides[3] = {row_bytes, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  if (H == 1) strides[1] = row_bytes * (cuuint64_t)rows;
+  if (B == 1) strides[2] = strides[1] * (cuuint64_t)H;
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// 32 x 32 fp32 boxes into a (BH, rows, cols) tensor whose rows are `row_stride` floats apart
+bool make_map_store_f32(CUtensorMap* m, void* base, int cols, int rows, int64_t row_stride,
+                        int64_t bh_stride, int BH) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)BH};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)bh_stride * 4};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool ok16(const void* ptr, int64_t a, int64_t b, int64_t c) {
+  return (reinterpret_cast<uintptr_t>(ptr) % 16 == 0) && a % 8 == 0 && b % 8 == 0 && c % 8 == 0;
+}
+
+bool device_is_sm100() {
+  static int cached = -1;
+  if (cached < 0) {
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
+    cached = (major == 10) ? 1 : 0;
+  }
+  return cached == 1;
+}
+
+// Per-device status word the kernels raise when a bounded wait gives up.
+__device__ int g_tc_status = 0;
+
+int* device_status_word() {
+  static int* words[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (words[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_tc_status) == cudaSuccess) words[dev] = static_cast<int*>(ptr);
+  }
+  return words[dev];
+}
+
+template <typename T, int D>
+cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
+  using L = Smem<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const int nqb = (p.m_end + BM - 1) / BM - p.m_begin / BM;
+  dim3 grid(nqb, p.Hq, p.B);
+  tc_fwd_kernel<T, D><<<grid, NTHREADS, L::alloc, s>>>(maps, p, device_status_word());
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_fwd_supported(const FwdParams& p, int dtype) {
+  (void)dtype;
+  if (p.D != 64 && p.D != 128) return false;
+  if (!device_is_sm100() || get_encode() == nullptr) return false;
+  if (p.m_begin % BM != 0 || p.m_end <= p.m_begin) return false;
+  if (!ok16(p.q, p.q_sb, p.q_sh, p.q_ss) || !ok16(p.k, p.k_sb, p.k_sh, p.k_ss) ||
+      !ok16(p.v, p.v_sb, p.v_sh, p.v_ss) || !ok16(p.o, p.o_sb, p.o_sh, p.o_ss))
+    return false;
+  if (p.scores != nullptr) {
+    if (!p.scores_f32 || p.N % 4 != 0 || reinterpret_cast<uintptr_t>(p.scores) % 16 != 0) return false;
+  }
+  if (p.s_scratch != nullptr) {
+    if (p.scores != nullptr) return false;
+    if (p.split % 32 != 0 || reinterpret_cast<uintptr_t>(p.s_scratch) % 16 != 0) return false;
+  }
+  return true;
+}
+
+cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
+  TcMaps maps;
+  const int q_rows = p.m_end - p.m_begin;
+  const char* qbase = static_cast<const char*>(p.q) + (int64_t)p.m_begin * p.q_ss * 2;
+  if (!make_map_bhsd(&maps.q, qbase, p.D, q_rows, p.Hq, p.B, p.q_ss, p.q_sh, p.q_sb, 128) ||
+      !make_map_bhsd(&maps.k, p.k, p.D, p.N, p.Hk, p.B, p.k_ss, p.k_sh, p.k_sb, 128) ||
+      !make_map_bhsd(&maps.v, p.v, p.D, p.N, p.Hk, p.B, p.v_ss, p.v_sh, p.v_sb, 128))
+    return cudaErrorInvalidValue;
+  maps.st = maps.q;
+  if (p.scores != nullptr) {
+    float* base = static_cast<float*>(p.scores) + (int64_t)p.m_begin * p.N;
+    if (!make_map_store_f32(&maps.st, base, p.N, q_rows, p.N, (int64_t)p.M * p.N, p.B * p.Hq))
+      return cudaErrorInvalidValue;
+  } else if (p.s_scratch != nullptr) {
+    const int rows = p.m_end - p.split;  // rows of the cross region inside the window
+    if (rows > 0 &&
+        !make_map_store_f32(&maps.st, p.s_scratch, p.split, rows, p.split, (int64_t)(p.M - p.split) * p.split,
+                            p.B * p.Hq))
+      return cudaErrorInvalidValue;
+  }
+  if (dtype == FAWS_FP16)
+    return p.D == 128 ? launch_fwd_t<__half, 128>(maps, p, s) : launch_fwd_t<__half, 64>(maps, p, s);
+  return p.D == 128 ? launch_fwd_t<__nv_bfloat16, 128>(maps, p, s) : launch_fwd_t<__nv_bfloat16, 64>(maps, p, s);
+}
+
+int tc_read_status(int reset) {
+  int* word = device_status_word();
+  if (word == nullptr) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (reset && v != 0) cudaMemset(word, 0, sizeof(int));
+  return v;
+}
+
 bool tc_colsoftmax_supported(const ColSoftmaxParams&, int) { return false; }
 cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams&, int, cudaStream_t) { return cudaErrorNotSupported; }
-}
+
+}  // namespace faws

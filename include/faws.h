@@ -195,6 +195,15 @@ size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split);
 int faws_reduce_ranks(const float* parts, int32_t n_ranks, int64_t count, float* out,
                       void* stream);
 
+/*
+ * The tcgen05 kernels bound every wait on an mbarrier (2 s).  A CTA that gives up
+ * raises a per-device status word, frees its TMEM and returns; its outputs are then
+ * invalid.  This call synchronises the device and returns that word (0 = no give-up,
+ * 1 = some wait gave up, -1 = the word could not be read); `reset` != 0 clears it.
+ * No counterpart in the reference.
+ */
+int faws_device_status(int32_t reset);
+
 /* Which kernel family the calling thread's last successful call used
  * (FAWS_BACKEND_GENERIC or FAWS_BACKEND_TCGEN05; 0 before any call) and how
  * many kernels this library has launched from this process. */

@@ -176,7 +176,7 @@ def linear_row_sum(q, k, causal, sm_scale=None, p_seq=0):
 
 # ---------------------------------------------------------------------------
 # Tolerances (written once, used by every parity test).
-#   out                      : max abs <= 2e-3
+#   out                      : max abs <= 2e-3 (+ bf16_out_slack when the tensors are bf16)
 #   scores                   : |x-ref| <= 1e-3*|ref| + 1e-4, masked entries bit-exact
 #   sums (fp32 accumulation) : |x-ref| <= 1e-3*|ref| + 1e-3*rms(ref)
 # ---------------------------------------------------------------------------
@@ -185,9 +185,26 @@ REL_TOL = 1e-3
 SCORES_ATOL = 1e-4
 
 
-def check_out(x, ref):
-    err = (x.float() - ref.float()).abs().max().item()
-    return err <= OUT_ATOL, err
+def bf16_out_slack(scores, v, out):
+    """Extra |out| error a bf16 pipeline cannot avoid, per element: the stored result is
+    rounded to bf16 (<= 2^-8 |out|, bf16 keeps 8 significant bits) and the softmax weights
+    are rounded to bf16 before the P.V product, as the reference kernel does
+    (flash.py:470 ``p.to(input_dtype)``), which moves out by <= 2^-9 * sum_j w_ij |v_j|.
+    fp16 (11 bits) stays inside the plain 2e-3 bound, so this is used for bf16 only."""
+    Hq, Hk = scores.shape[1], v.shape[1]
+    w = softmax_weights(scores)
+    absv = _expand_kv(v.float().abs(), Hq // Hk)
+    return out.float().abs() * 2.0 ** -8 + torch.matmul(w, absv) * 2.0 ** -9
+
+
+def check_out(x, ref, slack=None):
+    """max |x - ref| <= 2e-3 (+ ``slack`` from bf16_out_slack for bf16 tensors)."""
+    diff = (x.float() - ref.float()).abs()
+    tol = torch.full_like(diff, OUT_ATOL)
+    if slack is not None:
+        tol = tol + slack
+    viol = (diff - tol).max().item()
+    return viol <= 0, diff.max().item()
 
 
 def check_sum(x, ref):

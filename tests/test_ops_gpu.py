@@ -33,8 +33,8 @@ def _oracle(q, k, v, causal):
     return orc.naive_attention_with_scores(q, k, v, causal, p_seq=N - M)
 
 
-def _check_out(o, ref):
-    ok, err = orc.check_out(o.cpu(), ref)
+def _check_out(o, ref, slack=None):
+    ok, err = orc.check_out(o.cpu(), ref, slack if o.dtype == torch.bfloat16 else None)
     assert ok, f"out max abs err {err}"
 
 
@@ -58,6 +58,8 @@ def test_all_entry_points(shape, causal, dtype, backend):
     ref_out, ref_scores = _oracle(q, k, v, causal)
     qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
     kw = dict(backend=backend)
+    slack = orc.bf16_out_slack(ref_scores, v, ref_out) if dtype == torch.bfloat16 else None
+    _check_out = lambda o, ref: globals()["_check_out"](o, ref, slack)  # noqa: E731
 
     o, L, tot, _, _ = F.attention(qd, kd, vd, causal, return_log_normalizer=True, return_total_attention=True, **kw)
     _check_out(o, ref_out)
