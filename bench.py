@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the attention-with-scores hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-ops]
+
+Workload (config.workload = "cfg2"): fused attention_with_scores, fp16, B=1,
+Hq=Hkv=32, S=1024, D=128, causal, fp32 scores (1,32,1024,1024) -- the
+configuration the headline metric is quoted on.  One step = one call of the
+public operator on one batch of synthetic N(0,1) inputs.  With N > 1 ranks
+(torchrun, one process per GPU) every rank runs the same per-GPU workload on
+its own (batch x kv-head) units: weak scaling, no data-path collective.
+
+The JSON line carries the score-write rate (`value`, GB/s), the roofline of the
+dominant kernel, the same metric end to end from pinned host buffers (`e2e`),
+the CPU oracle timed on this host (`cpu_baseline`), sampled clocks, and a table
+of the other operators on their configurations (`ops`).
+
+`--impl reference` times the reference's own CPU path for this operator (the
+naive PyTorch attention, restated in oracle/oracle.py) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG2 = dict(B=1, Hq=32, Hk=32, S=1024, D=128, dtype=torch.float16, causal=True)
+N_SETS = 4  # rotating buffer sets: 4 x (134 MB scores + 8 MB out + 25 MB inputs) > 126 MB of L2
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm=float(d["hbm_gbs"]), tensor=float(d["bf16_tflops"]),
+                    tensor_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), src="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, src="fallback")
+
+
+def algorithmic(cfg, op="scores", split=None):
+    """FLOPs and bytes of one call: 4*pairs*D per (b, q head) (+2*extra pairs for a second q.k^T);
+    bytes = q, out, k, v once + the operator's fp32 outputs."""
+    B, Hq, Hk, S, D = cfg["B"], cfg["Hq"], cfg["Hk"], cfg["S"], cfg["D"]
+    pairs = S * (S + 1) // 2 if cfg["causal"] else S * S
+    extra = 0
+    out_bytes = 0
+    if op == "scores":
+        out_bytes = B * Hq * S * S * 4
+    elif op in ("row_sum",):
+        out_bytes = B * Hq * S * 4
+    elif op in ("col_sum", "col_sum_sequential"):
+        out_bytes = B * Hk * S * 4
+    elif op == "softmax_col_sum":
+        extra = pairs
+        out_bytes = B * Hk * S * 4
+    elif op == "cross_qk":
+        out_bytes = B * Hk * split * 4
+    elif op == "cross_softmax":
+        extra = (S - split) * split
+        out_bytes = B * Hk * split * 4
+    elif op == "cross_softmax_buffered":
+        out_bytes = B * Hk * split * 4 + 2 * 4 * B * Hq * (S - split) * split
+    flops = B * Hq * D * (4 * pairs + 2 * extra)
+    io = 2 * B * Hq * S * D * 2 + 2 * B * Hk * S * D * 2
+    return flops, io + out_bytes
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index), "-f", self.path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            os.unlink(self.path)
+        except Exception:
+            return out
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.strip().lower() == "active":
+                    reasons.add(name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def make_inputs(cfg, seed, device, S=None):
+    S = cfg["S"] if S is None else S
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(cfg["B"], cfg["Hq"], S, cfg["D"], generator=g).to(cfg["dtype"])
+    k = torch.randn(cfg["B"], cfg["Hk"], S, cfg["D"], generator=g).to(cfg["dtype"])
+    v = torch.randn(cfg["B"], cfg["Hk"], S, cfg["D"], generator=g).to(cfg["dtype"])
+    if cfg.get("vdist") == "uniform":
+        v = (torch.rand(cfg["B"], cfg["Hk"], S, cfg["D"], generator=g) * 2 - 1).to(cfg["dtype"])
+    elif cfg.get("vscale"):
+        v = (v.float() * cfg["vscale"]).to(cfg["dtype"])
+    if device is None:
+        return q, k, v
+    return q.to(device), k.to(device), v.to(device)
+
+
+def cpu_reference_time(cfg, runs):
+    """The reference's naive CPU path (oracle port) on the host cores: median seconds per call."""
+    from oracle import oracle as orc
+    q, k, v = make_inputs(cfg, 0, None)
+    q, k, v = q.float(), k.float(), v.float()
+    orc.naive_attention_with_scores(q, k, v, cfg["causal"])  # warm-up
+    ts = []
+    for _ in range(runs):
+        t0 = time.perf_counter()
+        orc.naive_attention_with_scores(q, k, v, cfg["causal"])
+        ts.append(time.perf_counter() - t0)
+    return ts
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    cfg = CFG2
+    flops, nbytes = algorithmic(cfg)
+    score_bytes = cfg["B"] * cfg["Hq"] * cfg["S"] * cfg["S"] * 4
+    ts = cpu_reference_time(cfg, max(1, args.warmup))  # warm-up calls
+    t0 = time.perf_counter()
+    ts = cpu_reference_time(cfg, args.steps)
+    total = sum(ts)
+    sec = total / args.steps
+    val = score_bytes / sec / 1e9
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": "attention_with_scores score-write rate", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2", "op": "attention_with_scores", "B": 1, "Hq": 32, "Hk": 32, "S": 1024,
+                   "D": 128, "causal": True},
+        "tflops": flops / sec / 1e12,
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"whole cfg2 problem, {args.steps} calls of the naive PyTorch path "
+                                   f"(oracle port) on {cores} threads of {os.cpu_count()} logical CPUs"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_op(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return statistics.median(a.elapsed_time(b) for a, b in evs)
+
+
+def ops_table(F, device, pk):
+    """The other operators on their benchmark configurations (median ms over a few calls)."""
+    rows = []
+    cfg3 = dict(B=1, Hq=28, Hk=4, S=4096, D=128, dtype=torch.bfloat16, causal=True, vscale=0.5)
+    cfg4 = dict(B=2, Hq=32, Hk=8, S=4096, D=128, dtype=torch.float16, causal=True)
+    plans = [
+        ("cfg3", cfg3, None, [("attention", F.attention), ("row_sum", F.attention_with_row_sum),
+                              ("col_sum", F.attention_with_col_sum),
+                              ("col_sum_sequential", F.attention_with_col_sum_sequential),
+                              ("softmax_col_sum", F.attention_with_softmax_col_sum)]),
+        ("cfg4", cfg4, 3072, [("cross_qk", F.attention_cross_token_qk_sum),
+                              ("cross_softmax", F.attention_cross_token_softmax_sum),
+                              ("cross_softmax_buffered", F.attention_cross_token_softmax_sum_buffered)]),
+    ]
+    for name, cfg, split, ops in plans:
+        q, k, v = make_inputs(cfg, 0, device)
+        for op, fn in ops:
+            if split is None:
+                call = lambda: fn(q, k, v, cfg["causal"])  # noqa: E731
+            else:
+                call = lambda: fn(q, k, v, split, cfg["causal"])  # noqa: E731
+            ms = time_op(call, 5, 3)
+            flops, nbytes = algorithmic(cfg, "scores" if op == "attention" else op, split)
+            if op == "attention":
+                nbytes -= cfg["B"] * cfg["Hq"] * cfg["S"] * cfg["S"] * 4
+            t_tensor = flops / (pk["tensor"] * 1e12)
+            t_hbm = nbytes / (pk["hbm"] * 1e9)
+            bound = "tensor" if t_tensor >= t_hbm else "hbm"
+            rows.append({"config": name, "op": op, "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                         "gbs": nbytes / (ms * 1e-3) / 1e9, "bound": bound,
+                         "frac": max(t_tensor, t_hbm) / (ms * 1e-3), "backend": F.last_backend()})
+        del q, k, v
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-ops", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    import flash_attn_with_score_b200 as F
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    cfg = CFG2
+    pk = peaks()
+    flops, nbytes = algorithmic(cfg)
+    score_bytes = cfg["B"] * cfg["Hq"] * cfg["S"] * cfg["S"] * 4
+
+    # rotating buffer sets so that every step's reads and writes miss L2
+    sets = []
+    for i in range(N_SETS):
+        q, k, v = make_inputs(cfg, 1000 * rank + i, device)
+        out = torch.empty_like(q)
+        scores = torch.empty(cfg["B"], cfg["Hq"], cfg["S"], cfg["S"], device=device, dtype=torch.float32)
+        sets.append((q, k, v, out, scores))
+
+    def step(i):
+        q, k, v, out, scores = sets[i % N_SETS]
+        F.attention_with_scores(q, k, v, cfg["causal"], out=out, scores=scores)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = F.launch_count()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(args.steps):
+        evs[i][0].record()
+        step(i)
+        evs[i][1].record()
+    t_end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = F.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_start.elapsed_time(t_end)
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    status = F.device_status()
+
+    t = torch.tensor([total_ms, kern_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, kern_ms = t.tolist()
+    ms_per_step = total_ms / args.steps
+
+    # end to end through the public API from pinned host buffers (H2D + op + D2H of out and scores)
+    hq, hk, hv = (x.pin_memory() for x in make_inputs(cfg, 7 + rank, None))
+    h_out = torch.empty(hq.shape, dtype=hq.dtype).pin_memory()
+    h_scores = torch.empty(cfg["B"], cfg["Hq"], cfg["S"], cfg["S"], dtype=torch.float32).pin_memory()
+    dq, dk, dv, dout, dscores = sets[0]
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        F.attention_with_scores(dq, dk, dv, cfg["causal"], out=dout, scores=dscores)
+        h_out.copy_(dout, non_blocking=True)
+        h_scores.copy_(dscores, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    te = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = te.item() / e2e_steps
+    h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv))
+    d2h = h_out.numel() * h_out.element_size() + h_scores.numel() * 4
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": "attention_with_scores score-write rate", "value": world * score_bytes / (ms_per_step * 1e-3) / 1e9,
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "cfg2", "op": "attention_with_scores", "B": 1, "Hq": 32, "Hk": 32, "S": 1024,
+                   "D": 128, "causal": True, "scores": "fp32, -inf at hidden entries",
+                   "per_gpu_units": 32, "l2": f"{N_SETS} rotating buffer sets (>126 MB L2)"},
+        "tflops": world * flops / (ms_per_step * 1e-3) / 1e12,
+        "roofline": {"bound": "hbm", "achieved": nbytes / (kern_ms * 1e-3) / 1e9, "peak": pk["hbm"],
+                     "unit": "GB/s", "frac": nbytes / (kern_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
+                     "peak_source": pk["src"], "kernel": "tc_fwd_kernel<half,128> (scores hook)",
+                     "algorithmic_bytes": nbytes, "kernel_ms": kern_ms},
+        "e2e": {"value": world * score_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": launches, "backend": F.last_backend(), "device_status": status, "clocks": clocks,
+    }
+    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_path):
+        try:
+            line["roofline"]["traffic"] = json.load(open(traffic_path)).get("cfg2_scores_bytes_per_launch")
+        except Exception:
+            pass
+    if world == 1 and not args.no_cpu:
+        ts = cpu_reference_time(cfg, 5)
+        sec = statistics.median(ts)
+        cores = torch.get_num_threads()
+        line["cpu_baseline"] = {"value": score_bytes / sec / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                "ms": sec * 1e3,
+                                "sample": f"whole cfg2 problem, median of 5 calls of the naive PyTorch path "
+                                          f"(oracle port), {cores} threads of {os.cpu_count()} logical CPUs"}
+    if world == 1 and not args.no_ops:
+        try:
+            line["ops"] = ops_table(F, device, pk)
+        except Exception as e:  # keep the headline line even if a side measurement fails
+            line["ops_error"] = repr(e)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -49,6 +49,12 @@ def backend(request):
     return request.param
 
 
+@pytest.fixture(autouse=True)
+def _no_wait_gave_up():
+    yield
+    assert F.device_status() == 0, "a bounded mbarrier wait gave up inside a tcgen05 kernel"
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
@@ -180,3 +186,50 @@ def test_kernel_golden_fixtures(golden_dir):
             o, x = fn(q, k, v, *args, causal)
             ok, viol = orc.check_sum(x.cpu(), t(key))
             assert ok, (os.path.basename(path), key, viol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
+@pytest.mark.parametrize("shape", [(1, 2, 1, 256, 256, 128), (1, 2, 2, 200, 328, 64), (2, 6, 2, 640, 640, 128),
+                                   (1, 1, 1, 128, 1000, 128), (1, 2, 2, 1000, 1000, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_tcgen05_family_is_used_and_matches(shape, causal, dtype):
+    """Forces the tcgen05 kernels (an unsupported problem would raise) on aligned and ragged shapes."""
+    B, Hq, Hk, M, N, D = shape
+    q, k, v = _inputs(shape, dtype, seed=11)
+    ref_out, ref_scores = _oracle(q, k, v, causal)
+    slack = orc.bf16_out_slack(ref_scores, v, ref_out) if dtype == torch.bfloat16 else None
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    kw = dict(backend="tcgen05")
+    o, s = F.attention_with_scores(qd, kd, vd, causal, **kw)
+    assert F.last_backend() == "tcgen05"
+    _check_out(o, ref_out, slack)
+    ok, viol, ok_mask = orc.check_scores(s.cpu(), ref_scores)
+    assert ok_mask and ok, viol
+    o, L, _, _, _ = F.attention(qd, kd, vd, causal, return_log_normalizer=True, **kw)
+    _check_out(o, ref_out, slack)
+    Lref = orc.log_normalizer(ref_scores)
+    fin = torch.isfinite(Lref)
+    assert torch.equal(torch.isneginf(L.cpu()), ~fin) and (L.cpu()[fin] - Lref[fin]).abs().max() < 2e-3
+    o, rs = F.attention_with_row_sum(qd, kd, vd, causal, **kw)
+    _check_sum(rs, orc.row_sum(ref_scores), "row_sum")
+    col_ref = orc.group_sum(orc.col_sum(ref_scores), Hk)
+    o, cs = F.attention_with_col_sum(qd, kd, vd, causal, **kw)
+    _check_out(o, ref_out, slack)
+    _check_sum(cs, col_ref, "col_sum")
+    o, cs2 = F.attention_with_col_sum_sequential(qd, kd, vd, causal, **kw)
+    _check_out(o, ref_out, slack)
+    assert torch.equal(cs, cs2)
+    split = (min(M, N) // 2 // 32) * 32
+    o, xq = F.attention_cross_token_qk_sum(qd, kd, vd, split, causal, **kw)
+    _check_sum(xq, orc.group_sum(orc.cross_token_qk_sum(ref_scores, split), Hk), "cross_qk")
+    # pass 1 on tcgen05 (out, L, score scratch), pass 2 on whichever family fits
+    o, xs = F.attention_cross_token_softmax_sum(qd, kd, vd, split, causal)
+    _check_out(o, ref_out, slack)
+    xs_ref = orc.group_sum(orc.cross_token_softmax_sum(ref_scores, split), Hk)
+    _check_sum(xs, xs_ref, "cross_softmax")
+    o, xb = F.attention_cross_token_softmax_sum_buffered(qd, kd, vd, split, causal)
+    _check_out(o, ref_out, slack)
+    _check_sum(xb, xs_ref, "cross_softmax_buffered")
+    o, sc = F.attention_with_softmax_col_sum(qd, kd, vd, causal)
+    _check_sum(sc, orc.group_sum(orc.softmax_col_sum(ref_scores), Hk), "softmax_col_sum")
