@@ -236,85 +236,93 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     unsigned char* p_smem = smem + L::p_off;
     int n_stage = 0;  // staging-buffer uses so far (this warp)
 
-    float m_run = FAWS_NEG_INF, l_run = 0.f, rs = 0.f;
+    float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
     bool alive = true;
 
-    for (int it = 0; it < nt; ++it) {
-      const int n0 = tile_of(it) * BN;
-      const int buf = it & 1;
-      if (!mbar_wait(&bars->s_full[buf], (it >> 1) & 1, abort_flag)) { alive = false; break; }
-      tc_fence_after();
-      const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= m0 + p.p_seq));
+    // One key tile.  The row's 128 scores are read from TMEM once and stay in registers for
+    // both passes.  kMasked = false is the common case of a fully visible tile.
+    auto tile_body = [&](auto masked_tag, int it, int n0, int buf) -> bool {
+      constexpr bool kMasked = decltype(masked_tag)::value;
+      uint32_t r[128];
       const uint32_t t_s = t_lane + (uint32_t)(buf * BN);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
+      tmem_wait_ld();
+      int nvis = 128;  // visible columns form a prefix of the tile's row
+      if (kMasked) {
+        int lim = p.N;
+        if (p.causal) lim = min(lim, i + p.p_seq + 1);
+        nvis = max(0, min(128, lim - n0));
+      }
+#define FAWS_VIS(x) (!kMasked || (x) < nvis)
 
-      // ---- pass 1: running max and the score-tile hooks
-      float mx = FAWS_NEG_INF;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + c * 32, r);
-        tmem_wait_ld();
-        const int jb = n0 + c * 32;
-        uint32_t vis_mask = 0xffffffffu;
-        if (!full_vis) {
-          vis_mask = 0;
+      // ---- pass 1: row max (4 independent chains) and the score-tile hooks
+      float a0 = FAWS_NEG_INF, a1 = FAWS_NEG_INF, a2 = FAWS_NEG_INF, a3 = FAWS_NEG_INF;
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const int j = jb + x;
-            if (j < p.N && (!p.causal || j <= i + p.p_seq)) vis_mask |= (1u << x);
-          }
+      for (int x = 0; x < 128; x += 4) {
+        a0 = fmaxf(a0, FAWS_VIS(x) ? __uint_as_float(r[x]) : FAWS_NEG_INF);
+        a1 = fmaxf(a1, FAWS_VIS(x + 1) ? __uint_as_float(r[x + 1]) : FAWS_NEG_INF);
+        a2 = fmaxf(a2, FAWS_VIS(x + 2) ? __uint_as_float(r[x + 2]) : FAWS_NEG_INF);
+        a3 = fmaxf(a3, FAWS_VIS(x + 3) ? __uint_as_float(r[x + 3]) : FAWS_NEG_INF);
+      }
+      const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * scale_log2;  // sm_scale > 0
+
+      if (p.row_sum != nullptr) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int x = 0; x < 128; x += 4) {
+          s0 += FAWS_VIS(x) ? __uint_as_float(r[x]) : 0.f;
+          s1 += FAWS_VIS(x + 1) ? __uint_as_float(r[x + 1]) : 0.f;
+          s2 += FAWS_VIS(x + 2) ? __uint_as_float(r[x + 2]) : 0.f;
+          s3 += FAWS_VIS(x + 3) ? __uint_as_float(r[x + 3]) : 0.f;
         }
+        rs_raw += (s0 + s1) + (s2 + s3);
+      }
+      if (store_scores || store_scratch) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const float raw = __uint_as_float(r[x]);
-          mx = fmaxf(mx, ((vis_mask >> x) & 1u) ? raw * scale_log2 : FAWS_NEG_INF);
-        }
-        if (p.row_sum != nullptr) {
+        for (int c = 0; c < 4; ++c) {
+          const int jb = n0 + c * 32;
+          const bool do_scratch = store_scratch && (m0 + lg * 32 >= p.split) && (jb < p.split);
+          if (store_scores || do_scratch) {
+            unsigned char* sb = stage + (n_stage & 1) * 4096;
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
 #pragma unroll
-          for (int x = 0; x < 32; ++x)
-            rs += ((vis_mask >> x) & 1u) ? __uint_as_float(r[x]) * scale : 0.f;
-        }
-        const bool do_scores = store_scores;
-        const bool do_scratch = store_scratch && (m0 + lg * 32 >= p.split) && (jb < p.split);
-        if (do_scores || do_scratch) {
-          unsigned char* sb = stage + (n_stage & 1) * 4096;
-          if (lane == 0) tma_store_wait_read<1>();
-          __syncwarp();
+            for (int cc = 0; cc < 8; ++cc) {
+              float4 val;
+              float* vp = reinterpret_cast<float*>(&val);
 #pragma unroll
-          for (int cc = 0; cc < 8; ++cc) {
-            float4 val;
-            float* vp = reinterpret_cast<float*>(&val);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int x = cc * 4 + e;
-              const float sc = __uint_as_float(r[x]) * scale;
-              vp[e] = (do_scratch || ((vis_mask >> x) & 1u)) ? sc : masked_f;
+              for (int e = 0; e < 4; ++e) {
+                const int x = c * 32 + cc * 4 + e;
+                const float sc = __uint_as_float(r[x]) * scale;
+                vp[e] = (store_scratch || FAWS_VIS(x)) ? sc : masked_f;
+              }
+              *reinterpret_cast<float4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = val;
             }
-            *reinterpret_cast<float4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = val;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (store_scores) tma_store_3d(&maps.st, sb, jb, m0 + lg * 32 - p.m_begin, bh);
+              else tma_store_3d(&maps.st, sb, jb, m0 + lg * 32 - p.split, bh);
+              tma_store_commit();
+            }
+            ++n_stage;
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int r0 = m0 + lg * 32 - p.m_begin;
-            if (do_scores) tma_store_3d(&maps.st, sb, jb, r0, bh);
-            else tma_store_3d(&maps.st, sb, jb, m0 + lg * 32 - p.split, bh);
-            tma_store_commit();
-          }
-          ++n_stage;
-        }
-        if (p.col_partial != nullptr) {
-          float cv[32];
-          const bool contrib = row_ok && i >= p.col_row_begin;
-#pragma unroll
-          for (int x = 0; x < 32; ++x)
-            cv[x] = (contrib && ((vis_mask >> x) & 1u)) ? __uint_as_float(r[x]) * scale : 0.f;
-          warp_column_sums(cv, lane);
-          colbuf[(buf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
         }
       }
       if (p.col_partial != nullptr) {
+        const bool contrib = row_ok && i >= p.col_row_begin;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float cv[32];
+#pragma unroll
+          for (int x = 0; x < 32; ++x)
+            cv[x] = (contrib && FAWS_VIS(c * 32 + x)) ? __uint_as_float(r[c * 32 + x]) * scale : 0.f;
+          warp_column_sums(cv, lane);
+          colbuf[(buf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
+        }
         mbar_arrive(&bars->col_ready);
-        if (!mbar_wait(&bars->col_ready, it & 1, abort_flag)) { alive = false; break; }
+        if (!mbar_wait(&bars->col_ready, it & 1, abort_flag)) return false;
         if (part_on && n0 + row < p.ncols_pad) {
           const float* cb = colbuf + buf * 512;
           // fixed order: the warps that own rows 0-31, 32-63, 64-95, 96-127
@@ -328,60 +336,69 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       const bool need = m_new > m_run + kRescaleThreshold;
       float alpha = 1.f;
       if (need) {
-        alpha = exp2f(m_run - m_new);
+        alpha = fast_exp2(m_run - m_new);
         m_run = m_new;
         l_run *= alpha;
       }
       if (it > 0) {
-        if (!mbar_wait(&bars->pv_done, (it - 1) & 1, abort_flag)) { alive = false; break; }
+        if (!mbar_wait(&bars->pv_done, (it - 1) & 1, abort_flag)) return false;
         tc_fence_after();
         if (__any_sync(0xffffffffu, need)) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, r);
+            uint32_t ro[32];
+            tmem_ld32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, ro);
             tmem_wait_ld();
 #pragma unroll
-            for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
-            tmem_st32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, r);
+            for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
+            tmem_st32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, ro);
           }
           tmem_wait_st();
         }
       }
 
-      // ---- pass 2: P = exp2(t - m), row sum of P, P -> smem (K-major, 128B swizzle)
-      const float m_use = (m_run == FAWS_NEG_INF) ? 0.f : m_run;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_s + c * 32, r);
-        tmem_wait_ld();
-        const int jb = n0 + c * 32;
-        float pr[32];
+      // ---- pass 2: P = exp2(s*scale*log2e - m), row sum of P, P -> smem (K-major, 128B swizzle)
+      const float neg_m = (m_run == FAWS_NEG_INF) ? 0.f : -m_run;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int j = jb + x;
-          const bool vis = full_vis || (j < p.N && (!p.causal || j <= i + p.p_seq));
-          const float t = vis ? __uint_as_float(r[x]) * scale_log2 - m_use : FAWS_NEG_INF;
-          pr[x] = exp2f(t);
-          l_run += pr[x];
-        }
-        unsigned char* prow = p_smem + (c >> 1) * L::kSub + row * 128;
+      for (int g = 0; g < 16; ++g) {  // 8 columns = one 16-byte chunk of the P row
+        float e[8];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w;
-          w.x = pack2<T>(pr[g * 8 + 0], pr[g * 8 + 1]);
-          w.y = pack2<T>(pr[g * 8 + 2], pr[g * 8 + 3]);
-          w.z = pack2<T>(pr[g * 8 + 4], pr[g * 8 + 5]);
-          w.w = pack2<T>(pr[g * 8 + 6], pr[g * 8 + 7]);
-          const int cc = (c & 1) * 4 + g;
-          *reinterpret_cast<uint4*>(prow + ((cc ^ (row & 7)) << 4)) = w;
+        for (int y = 0; y < 8; ++y) {
+          const int x = g * 8 + y;
+          const float pe = fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, neg_m));
+          e[y] = FAWS_VIS(x) ? pe : 0.f;
         }
+        l0 += e[0] + e[4];
+        l1 += e[1] + e[5];
+        l2 += e[2] + e[6];
+        l3 += e[3] + e[7];
+        uint4 w;
+        w.x = pack2<T>(e[0], e[1]);
+        w.y = pack2<T>(e[2], e[3]);
+        w.z = pack2<T>(e[4], e[5]);
+        w.w = pack2<T>(e[6], e[7]);
+        const int cc = g & 7;
+        *reinterpret_cast<uint4*>(p_smem + (g >> 3) * L::kSub + row * 128 + ((cc ^ (row & 7)) << 4)) = w;
       }
+      l_run += (l0 + l1) + (l2 + l3);
+#undef FAWS_VIS
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->p_ready);
+      return true;
+    };
+
+    for (int it = 0; it < nt; ++it) {
+      const int n0 = tile_of(it) * BN;
+      const int buf = it & 1;
+      if (!mbar_wait(&bars->s_full[buf], (it >> 1) & 1, abort_flag)) { alive = false; break; }
+      tc_fence_after();
+      const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= m0 + p.p_seq));
+      const bool ok = full_vis ? tile_body(std::false_type{}, it, n0, buf) : tile_body(std::true_type{}, it, n0, buf);
+      if (!ok) { alive = false; break; }
     }
+    const float rs = rs_raw * scale;
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
     if (alive && nt > 0) {
@@ -555,6 +572,7 @@ cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
 bool tc_fwd_supported(const FwdParams& p, int dtype) {
   (void)dtype;
   if (p.D != 64 && p.D != 128) return false;
+  if (!(p.sm_scale > 0.f)) return false;  // the row max is taken on unscaled scores
   if (!device_is_sm100() || get_encode() == nullptr) return false;
   if (p.m_begin % BM != 0 || p.m_end <= p.m_begin) return false;
   if (!ok16(p.q, p.q_sb, p.q_sh, p.q_ss) || !ok16(p.k, p.k_sb, p.k_sh, p.k_ss) ||

@@ -47,29 +47,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Bounded wait: gives up after `limit_ns` or as soon as *abort_flag is set by
-// another thread of the CTA.  Returns false on give-up (and sets the flag).
+// Bounded wait: gives up after `limit_cycles` SM cycles (about 2 s) or as soon as
+// *abort_flag is set by another thread of the CTA.  Returns false on give-up (and
+// sets the flag).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          uint64_t limit_ns = 2000000000ull) {
+                                          long long limit_cycles = 4000000000ll) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
+    if ((++spins & 255u) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
     }
   }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // ---------------------------------------------------------------- fences
