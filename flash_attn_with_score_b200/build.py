@@ -40,6 +40,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         "-I", os.path.join(ROOT, "include"), "-I", CSRC,
         "-o", LIB,
     ] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcuda"]
+    if os.environ.get("FAWS_NVCC_FLAGS"):
+        cmd[1:1] = os.environ["FAWS_NVCC_FLAGS"].split()
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

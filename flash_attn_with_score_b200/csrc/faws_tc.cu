@@ -1,25 +1,29 @@
 // tcgen05 / TMEM / TMA kernels (sm_100a) of the attention-with-scores family.
 //
-// Forward kernel: one CTA = 128 query rows of one (batch, query head), key tiles
-// of 128.  Warp roles:
-//   warp 0      TMA producer: Q once, then K and V tiles through 2-stage rings
-//   warp 1      allocates TMEM; one lane issues the tcgen05 MMAs
-//               S = Q.K^T (fp32, TMEM, double buffered) and O += P.V (fp32, TMEM)
-//   warps 2..5  softmax: thread r owns query row r (TMEM lane r).  It reads S twice
-//               (pass 1: running max + score-tile hooks, pass 2: exp2 and P), rescales
-//               O in TMEM only when the running max moved by more than 2^8, and writes
-//               P as 16-bit into a 128B-swizzled smem tile for the second MMA.
+// Forward kernel: one CTA = 256 query rows (two tiles of 128) of one (batch, query
+// head); key tiles of 128 shared by both query tiles.  Warp roles (12 warps):
+//   warp 0       TMA producer: both Q tiles once, then K and V tiles through one 3-slot ring
+//   warp 1       allocates TMEM; one lane issues the tcgen05 MMAs.  Per query tile t:
+//                S_t = Q_t.K^T (fp32, TMEM) and O_t += P_t.V (fp32, TMEM; P_t is read
+//                from TMEM, where it overwrites S_t).  The two query tiles alternate, so
+//                the tensor pipe works on one while the other is in its softmax.
+//   warps 2,3    idle (they only give their registers to the softmax warps)
+//   warps 4..7   softmax of query tile 0; warps 8..11 softmax of query tile 1.
+//                Thread r owns query row r (TMEM lane r): it reads the row's 128 scores
+//                once, keeps them in registers for the running max and for exp2, rescales
+//                O in TMEM only when the running max moved by more than 2^8, and writes P
+//                back to TMEM as 16-bit pairs.
 // Score-tile hooks (what attention_with_scores.py:141-162, attention_with_row_sum.py:146-156,
 // attention_with_col_sum.py:170-191 add to the FlashAttention loop):
 //   scores      fp32 tile staged per warp (32x32, swizzled) and written with TMA stores;
 //               key tiles the causal loop never visits are filled from one constant tile
 //   row sum     per-thread running sum
 //   column sum  per-warp transpose-reduce with shuffles, 4 warps combined through smem,
-//               one partial row per query block (summed later in fixed order)
+//               one partial row per 128-row query tile (summed later in fixed order)
 //   scratch     the cross region's scores (buffered cross-token variant) via TMA stores
 //
-// Every mbarrier wait is bounded (2 s); on give-up the CTA raises a flag in *status,
-// lets in-flight copies drain, frees its TMEM and returns.
+// Every mbarrier wait is bounded (about 2 s); on give-up the CTA raises a flag in
+// *status, lets in-flight copies drain, frees its TMEM and returns.
 #include <cuda.h>
 
 #include <cstdio>
@@ -33,15 +37,34 @@ namespace faws {
 namespace {
 using namespace ptx;
 
-constexpr int BM = kTcBlockM;
+constexpr int BM = kTcBlockM;   // rows of one query tile
 constexpr int BN = kTcBlockN;
-constexpr int NTHREADS = 192;
-constexpr int KV_STAGES = 2;
+constexpr int CTA_ROWS = 2 * BM;
+constexpr int NTHREADS = 384;
+constexpr int KV_SLOTS = 3;
 constexpr int TMEM_COLS = 512;
+// setmaxnreg budget: the CTA is launched with 168 registers per thread (384 threads, one
+// CTA per SM); after re-allocation the total must not exceed that pool, otherwise the
+// .inc never returns.
+constexpr int REGS_LAUNCH = 168;
+constexpr int REGS_AUX = 40;
+constexpr int REGS_SOFTMAX = 232;
+static_assert(128 * REGS_AUX + 256 * REGS_SOFTMAX <= REGS_LAUNCH * NTHREADS, "setmaxnreg would block");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #define FAWS_NEG_INF (__int_as_float(0xff800000))
+
+#ifdef FAWS_TRACE
+__device__ long long g_trace[3 * 4096];
+#define TRACE_DECL(role) const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0); int tr_n = 0; long long* tr_buf = g_trace + (role) * 4096;
+#define TRACE(tag) do { if (tr_on && tr_n < 2040) { tr_buf[2 * tr_n] = (tag); tr_buf[2 * tr_n + 1] = clock64(); ++tr_n; } } while (0)
+#define TRACE_END() do { if (tr_on) { tr_buf[2 * tr_n] = -1; } } while (0)
+#else
+#define TRACE_DECL(role)
+#define TRACE(tag)
+#define TRACE_END()
+#endif
 
 struct TcMaps {
   CUtensorMap q, k, v, st;  // st: scores (or score-scratch) store map
@@ -51,24 +74,21 @@ template <int D>
 struct Smem {
   static constexpr int kTile = 128 * D * 2;  // one Q / K / V tile
   static constexpr int kSub = 128 * 128;     // one 64-element-wide sub-tile: 128 rows x 128 B
-  static constexpr int q_off = 0;
-  static constexpr int k_off = q_off + kTile;
-  static constexpr int v_off = k_off + KV_STAGES * kTile;
-  static constexpr int p_off = v_off + KV_STAGES * kTile;  // P: 128 x 128 x 16 bit
-  static constexpr int stage_off = p_off + 2 * kSub;       // 4 warps x 2 x 4 KB
-  static constexpr int bar_off = stage_off + 4 * 2 * 4096;
+  static constexpr int q_off = 0;                          // 2 query tiles
+  static constexpr int kv_off = q_off + 2 * kTile;         // K/V ring
+  static constexpr int stage_off = kv_off + KV_SLOTS * kTile;  // 8 warps x 2 x 4 KB
+  static constexpr int bar_off = stage_off + 8 * 2 * 4096;
   static constexpr int total = bar_off + 256;
   static constexpr int alloc = total + 1024;  // slack to align the base to 1024 B
 };
 
 struct Bars {
   uint64_t q_full;
-  uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
-  uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-  uint64_t s_full[2];
-  uint64_t p_ready;
-  uint64_t pv_done;
-  uint64_t col_ready;  // column-sum hook: the 4 softmax warps' partial rows are in smem
+  uint64_t kv_full[KV_SLOTS], kv_empty[KV_SLOTS];
+  uint64_t s_full[2];     // per query tile: S_t written by the tensor pipe
+  uint64_t p_ready[2];    // per query tile: P_t written by its 128 softmax threads
+  uint64_t col_ready[2];  // per query tile: column-sum partial rows of its 4 warps are in smem
+  uint64_t o_done;        // every MMA of the CTA has completed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -98,7 +118,10 @@ __device__ __forceinline__ void warp_column_sums(float (&v)[32], int lane) {
   }
 }
 
-template <typename T, int D>
+// Score-tile hook compiled into a kernel instance (one per operator family).
+enum Hook : int { kHookNone = 0, kHookScores = 1, kHookRowSum = 2, kHookColPart = 3, kHookScratch = 4 };
+
+template <typename T, int D, int HOOK>
 __global__ void __launch_bounds__(NTHREADS, 1)
 tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __restrict__ status) {
   using L = Smem<D>;
@@ -109,30 +132,39 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nqb = gridDim.x;
-  const int qb_rel = nqb - 1 - (int)blockIdx.x;  // heaviest (last) causal blocks first
-  const int qb_abs = p.m_begin / BM + qb_rel;
-  const int m0 = qb_abs * BM;
+  const int ncb = gridDim.x;
+  const int cb_rel = ncb - 1 - (int)blockIdx.x;  // heaviest (last) causal blocks first
+  const int m0 = p.m_begin + cb_rel * CTA_ROWS;
+  const int cb_abs = m0 / CTA_ROWS;
   const int h = blockIdx.y, b = blockIdx.z, hk = h / p.G;
   const int bh = b * p.Hq + h;
 
-  int hi = p.N;
-  if (p.causal) hi = max(0, min(p.N, p.p_seq + min(m0 + BM, p.m_end)));
-  const int nt = (hi + BN - 1) / BN;
+  // key tiles each query tile visits (0 for a tile that lies outside the row window)
+  int nt_q[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r0 = m0 + t * BM;
+    int hi = 0;
+    if (r0 < p.m_end) {
+      hi = p.N;
+      if (p.causal) hi = max(0, min(p.N, p.p_seq + min(r0 + BM, p.m_end)));
+    }
+    nt_q[t] = (hi + BN - 1) / BN;
+  }
+  const int nt = max(nt_q[0], nt_q[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->k_empty[s], 1);
-      mbar_init(&bars->v_full[s], 1);
-      mbar_init(&bars->v_empty[s], 1);
+    for (int s = 0; s < KV_SLOTS; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
     }
-    mbar_init(&bars->s_full[0], 1);
-    mbar_init(&bars->s_full[1], 1);
-    mbar_init(&bars->p_ready, 128);
-    mbar_init(&bars->pv_done, 1);
-    mbar_init(&bars->col_ready, 128);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_ready[t], 128);
+      mbar_init(&bars->col_ready[t], 128);
+    }
+    mbar_init(&bars->o_done, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&maps.q);
@@ -147,107 +179,152 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  const uint32_t tmem_o = tmem_base + 256;
 
   auto tile_of = [&](int it) -> int {
     if (p.schedule == kReverse) return nt - 1 - it;
-    if (p.schedule == kRoundRobin) return (qb_abs + it) % nt;
+    if (p.schedule == kRoundRobin) return (cb_abs + it) % nt;
     return it;
   };
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      mbar_arrive_expect_tx(&bars->q_full, L::kTile);
-      for (int c = 0; c < D / 64; ++c)
-        tma_load_4d(smem + L::q_off + c * L::kSub, &maps.q, &bars->q_full, c * 64, m0 - p.m_begin, h, b);
-      for (int it = 0; it < nt; ++it) {
-        const int s = it % KV_STAGES, u = it / KV_STAGES;
-        const int n0 = tile_of(it) * BN;
-        if (!mbar_wait(&bars->k_empty[s], (u & 1) ^ 1, abort_flag)) break;
-        mbar_arrive_expect_tx(&bars->k_full[s], L::kTile);
+  if (warp < 4) {
+    reg_dealloc<REGS_AUX>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------- TMA producer
+      mbar_arrive_expect_tx(&bars->q_full, 2 * L::kTile);
+      for (int t = 0; t < 2; ++t)
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::k_off + s * L::kTile + c * L::kSub, &maps.k, &bars->k_full[s], c * 64, n0, hk, b);
-        if (!mbar_wait(&bars->v_empty[s], (u & 1) ^ 1, abort_flag)) break;
-        mbar_arrive_expect_tx(&bars->v_full[s], L::kTile);
+          tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
+                      m0 - p.m_begin + t * BM, h, b);
+      for (int idx = 0; idx < 2 * nt; ++idx) {  // K(0), V(0), K(1), V(1), ...
+        const int s = idx % KV_SLOTS, u = idx / KV_SLOTS;
+        const int n0 = tile_of(idx >> 1) * BN;
+        if (!mbar_wait(&bars->kv_empty[s], (u & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->kv_full[s], L::kTile);
+        const CUtensorMap* map = (idx & 1) ? &maps.v : &maps.k;
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::v_off + s * L::kTile + c * L::kSub, &maps.v, &bars->v_full[s], c * 64, n0, hk, b);
+          tma_load_4d(smem + L::kv_off + s * L::kTile + c * L::kSub, map, &bars->kv_full[s], c * 64, n0, hk, b);
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && nt > 0) {
+    } else if (warp == 1 && lane == 0 && nt > 0) {
+      // ---------------------------------------------------------- MMA issuer
       constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
       constexpr uint32_t idesc_qk = make_idesc_f16(128, BN, kFmt, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, 0, 1);
       const uint32_t q_addr = smem_u32(smem + L::q_off);
-      const uint32_t p_addr = smem_u32(smem + L::p_off);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
-      auto issue_qk = [&](int t) -> bool {
-        const int s = t % KV_STAGES, u = t / KV_STAGES;
-        if (!mbar_wait(&bars->k_full[s], u & 1, abort_flag)) return false;
+      const uint32_t kv_addr = smem_u32(smem + L::kv_off);
+      auto kv_wait = [&](int idx) -> bool {
+        if (!mbar_wait(&bars->kv_full[idx % KV_SLOTS], (idx / KV_SLOTS) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(smem + L::k_off + s * L::kTile);
-        const uint32_t d_tmem = tmem_base + (uint32_t)((t & 1) * BN);
+        return true;
+      };
+      // S_t = Q_t . K^T for the key tile in ring slot `slot`
+      auto issue_qk = [&](int t, int slot) {
+        const uint32_t k_addr = kv_addr + (uint32_t)(slot * L::kTile);
+        const uint32_t qa = q_addr + (uint32_t)(t * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
-          mma_ss(d_tmem, make_desc_sw128(q_addr + off, 16, 1024), make_desc_sw128(k_addr + off, 16, 1024),
-                 idesc_qk, kk > 0 ? 1u : 0u);
+          mma_ss(tmem_base + (uint32_t)(t * BN), make_desc_sw128(qa + off, 16, 1024),
+                 make_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
-        mma_commit(&bars->k_empty[s]);
-        mma_commit(&bars->s_full[t & 1]);
-        return true;
+        mma_commit(&bars->s_full[t]);
       };
-      if (ok) ok = issue_qk(0);
-      for (int it = 0; ok && it < nt; ++it) {
-        if (it + 1 < nt && !issue_qk(it + 1)) break;
-        const int s = it % KV_STAGES, u = it / KV_STAGES;
-        if (!mbar_wait(&bars->p_ready, it & 1, abort_flag)) break;
-        if (!mbar_wait(&bars->v_full[s], u & 1, abort_flag)) break;
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(smem + L::v_off + s * L::kTile);
+      // O_t (+)= P_t . V; P_t sits in the first 64 columns of S_t (two 16-bit values per column)
+      auto issue_pv = [&](int t, int slot, bool accumulate) {
+        const uint32_t v_addr = kv_addr + (uint32_t)(slot * L::kTile);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint32_t a_off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
-          mma_ss(tmem_o, make_desc_sw128(p_addr + a_off, 16, 1024),
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_ts(tmem_base + 256 + (uint32_t)(t * BN), tmem_base + (uint32_t)(t * BN) + (uint32_t)(kk * 8),
                  make_desc_sw128(v_addr + (uint32_t)(kk * 16 * 128), L::kSub, 1024), idesc_pv,
-                 (it > 0 || kk > 0) ? 1u : 0u);
-        }
-        mma_commit(&bars->v_empty[s]);
-        mma_commit(&bars->pv_done);
+                 (accumulate || kk > 0) ? 1u : 0u);
+      };
+      int cnt[2] = {0, 0};  // key tiles each query tile has been given so far
+      TRACE_DECL(2)
+      TRACE(0);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      if (ok) ok = kv_wait(0);
+      if (ok) {
+        const int t0 = tile_of(0);
+        if (t0 < nt_q[0]) issue_qk(0, 0);
+        if (t0 < nt_q[1]) issue_qk(1, 0);
+        mma_commit(&bars->kv_empty[0]);
       }
+      for (int it = 0; ok && it < nt; ++it) {
+        const int tk = tile_of(it);
+        const bool more = it + 1 < nt;
+        const int tk_next = more ? tile_of(it + 1) : 0;
+        const int v_slot = (2 * it + 1) % KV_SLOTS, k_slot = (2 * it + 2) % KV_SLOTS;
+        TRACE(10);
+        if (!(ok = kv_wait(2 * it + 1))) break;
+        TRACE(11);
+        if (tk < nt_q[0]) {
+          if (!(ok = mbar_wait(&bars->p_ready[0], cnt[0] & 1, abort_flag))) break;
+          TRACE(12);
+          tc_fence_after();
+          issue_pv(0, v_slot, cnt[0] > 0);
+          ++cnt[0];
+        }
+        if (more) {
+          if (!(ok = kv_wait(2 * it + 2))) break;
+          TRACE(13);
+          if (tk_next < nt_q[0]) issue_qk(0, k_slot);
+        }
+        if (tk < nt_q[1]) {
+          if (!(ok = mbar_wait(&bars->p_ready[1], cnt[1] & 1, abort_flag))) break;
+          TRACE(14);
+          tc_fence_after();
+          issue_pv(1, v_slot, cnt[1] > 0);
+          ++cnt[1];
+        }
+        mma_commit(&bars->kv_empty[v_slot]);
+        if (more) {
+          if (tk_next < nt_q[1]) issue_qk(1, k_slot);
+          mma_commit(&bars->kv_empty[k_slot]);
+        }
+      }
+      if (ok) mma_commit(&bars->o_done);
+      TRACE_END();
     }
   } else {
+    reg_alloc<REGS_SOFTMAX>();
     // ------------------------------------------------------------ softmax warps
-    const int lg = warp & 3;  // TMEM lane group this warp may touch
+    const int qt = (warp - 4) >> 2;  // query tile of this warpgroup
+    const int lg = warp & 3;         // TMEM lane group this warp may touch
     const int row = lg * 32 + lane;
-    const int i = m0 + row;
+    const int r_tile = m0 + qt * BM;  // first row of the query tile
+    const int i = r_tile + row;
+    const int my_nt = nt_q[qt];
     const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
+    const uint32_t t_s = t_lane + (uint32_t)(qt * BN);
+    const uint32_t t_o = t_lane + 256 + (uint32_t)(qt * BN);
     const bool row_ok = i >= p.m_begin && i < p.m_end;
     const float scale = p.sm_scale;
     const float scale_log2 = p.sm_scale * kLog2e;
-    unsigned char* stage = smem + L::stage_off + (warp - 2) * 8192;
-    float* colbuf = reinterpret_cast<float*>(smem + L::stage_off);  // [2][4][128], col hook only
-    const bool store_scores = p.scores != nullptr;
-    const bool store_scratch = p.s_scratch != nullptr;
-    const bool part_on = p.col_partial != nullptr && qb_abs >= p.qb_first;
+    unsigned char* stage = smem + L::stage_off + (warp - 4) * 8192;
+    float* colbuf = reinterpret_cast<float*>(smem + L::stage_off + qt * 32768);  // [2][4][128], col hook only
+    constexpr bool store_scores = HOOK == kHookScores;
+    constexpr bool store_scratch = HOOK == kHookScratch;
+    const int qb128 = r_tile / BM;
+    const bool part_on = HOOK == kHookColPart && qb128 >= p.qb_first && r_tile < p.m_end;
     const float masked_f = __uint_as_float(p.masked_bits);
-    unsigned char* p_smem = smem + L::p_off;
     int n_stage = 0;  // staging-buffer uses so far (this warp)
 
     float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
     bool alive = true;
+#ifdef FAWS_TRACE
+    const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0);
+    int tr_n = 0;
+    long long* tr_buf = g_trace + qt * 4096;
+#endif
 
     // One key tile.  The row's 128 scores are read from TMEM once and stay in registers for
     // both passes.  kMasked = false is the common case of a fully visible tile.
-    auto tile_body = [&](auto masked_tag, int it, int n0, int buf) -> bool {
+    auto tile_body = [&](auto masked_tag, int cnt, int n0) -> bool {
       constexpr bool kMasked = decltype(masked_tag)::value;
       uint32_t r[128];
-      const uint32_t t_s = t_lane + (uint32_t)(buf * BN);
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
       tmem_wait_ld();
+      TRACE(21);
       int nvis = 128;  // visible columns form a prefix of the tile's row
       if (kMasked) {
         int lim = p.N;
@@ -267,7 +344,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
       const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * scale_log2;  // sm_scale > 0
 
-      if (p.row_sum != nullptr) {
+      if constexpr (HOOK == kHookRowSum) {
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
         for (int x = 0; x < 128; x += 4) {
@@ -278,11 +355,11 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         }
         rs_raw += (s0 + s1) + (s2 + s3);
       }
-      if (store_scores || store_scratch) {
+      if constexpr (store_scores || store_scratch) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int jb = n0 + c * 32;
-          const bool do_scratch = store_scratch && (m0 + lg * 32 >= p.split) && (jb < p.split);
+          const bool do_scratch = store_scratch && (r_tile + lg * 32 >= p.split) && (jb < p.split);
           if (store_scores || do_scratch) {
             unsigned char* sb = stage + (n_stage & 1) * 4096;
             if (lane == 0) tma_store_wait_read<1>();
@@ -302,16 +379,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              if (store_scores) tma_store_3d(&maps.st, sb, jb, m0 + lg * 32 - p.m_begin, bh);
-              else tma_store_3d(&maps.st, sb, jb, m0 + lg * 32 - p.split, bh);
+              if (store_scores) tma_store_3d(&maps.st, sb, jb, r_tile + lg * 32 - p.m_begin, bh);
+              else tma_store_3d(&maps.st, sb, jb, r_tile + lg * 32 - p.split, bh);
               tma_store_commit();
             }
             ++n_stage;
           }
         }
       }
-      if (p.col_partial != nullptr) {
+      if constexpr (HOOK == kHookColPart) {
         const bool contrib = row_ok && i >= p.col_row_begin;
+        const int cbuf = cnt & 1;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           float cv[32];
@@ -319,19 +397,21 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           for (int x = 0; x < 32; ++x)
             cv[x] = (contrib && FAWS_VIS(c * 32 + x)) ? __uint_as_float(r[c * 32 + x]) * scale : 0.f;
           warp_column_sums(cv, lane);
-          colbuf[(buf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
+          colbuf[(cbuf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
         }
-        mbar_arrive(&bars->col_ready);
-        if (!mbar_wait(&bars->col_ready, it & 1, abort_flag)) return false;
+        mbar_arrive(&bars->col_ready[qt]);
+        if (!mbar_wait(&bars->col_ready[qt], cnt & 1, abort_flag)) return false;
         if (part_on && n0 + row < p.ncols_pad) {
-          const float* cb = colbuf + buf * 512;
+          const float* cb = colbuf + cbuf * 512;
           // fixed order: the warps that own rows 0-31, 32-63, 64-95, 96-127
           const float sum = ((cb[row] + cb[128 + row]) + cb[256 + row]) + cb[384 + row];
-          p.col_partial[((int64_t)bh * p.n_qb_part + (qb_abs - p.qb_first)) * (int64_t)p.ncols_pad + n0 + row] = sum;
+          p.col_partial[((int64_t)bh * p.n_qb_part + (qb128 - p.qb_first)) * (int64_t)p.ncols_pad + n0 + row] = sum;
         }
       }
 
-      // ---- running max, lazy rescale of O
+      // ---- running max, lazy rescale of O.  s_full for this tile was committed after this
+      // query tile's previous P.V MMA, so O_t is quiescent here.
+      TRACE(22);
       const float m_new = fmaxf(m_run, mx);
       const bool need = m_new > m_run + kRescaleThreshold;
       float alpha = 1.f;
@@ -340,28 +420,24 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         m_run = m_new;
         l_run *= alpha;
       }
-      if (it > 0) {
-        if (!mbar_wait(&bars->pv_done, (it - 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, need)) {
+      if (cnt > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t ro[32];
-            tmem_ld32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, ro);
-            tmem_wait_ld();
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ro[32];
+          tmem_ld32(t_o + c * 32, ro);
+          tmem_wait_ld();
 #pragma unroll
-            for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
-            tmem_st32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, ro);
-          }
-          tmem_wait_st();
+          for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
+          tmem_st32(t_o + c * 32, ro);
         }
       }
 
-      // ---- pass 2: P = exp2(s*scale*log2e - m), row sum of P, P -> smem (K-major, 128B swizzle)
+      TRACE(23);
+      // ---- pass 2: P = exp2(s*scale*log2e - m), row sum of P, P -> TMEM over S (16-bit pairs)
       const float neg_m = (m_run == FAWS_NEG_INF) ? 0.f : -m_run;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {  // 8 columns = one 16-byte chunk of the P row
+      for (int g = 0; g < 16; ++g) {
         float e[8];
 #pragma unroll
         for (int y = 0; y < 8; ++y) {
@@ -373,59 +449,68 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         l1 += e[1] + e[5];
         l2 += e[2] + e[6];
         l3 += e[3] + e[7];
-        uint4 w;
-        w.x = pack2<T>(e[0], e[1]);
-        w.y = pack2<T>(e[2], e[3]);
-        w.z = pack2<T>(e[4], e[5]);
-        w.w = pack2<T>(e[6], e[7]);
-        const int cc = g & 7;
-        *reinterpret_cast<uint4*>(p_smem + (g >> 3) * L::kSub + row * 128 + ((cc ^ (row & 7)) << 4)) = w;
+        r[g * 4 + 0] = pack2<T>(e[0], e[1]);
+        r[g * 4 + 1] = pack2<T>(e[2], e[3]);
+        r[g * 4 + 2] = pack2<T>(e[4], e[5]);
+        r[g * 4 + 3] = pack2<T>(e[6], e[7]);
       }
+      tmem_st32(t_s, reinterpret_cast<const uint32_t(&)[32]>(r[0]));
+      tmem_st32(t_s + 32, reinterpret_cast<const uint32_t(&)[32]>(r[32]));
+      TRACE(24);
+      tmem_wait_st();
       l_run += (l0 + l1) + (l2 + l3);
 #undef FAWS_VIS
-      fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&bars->p_ready);
+      mbar_arrive(&bars->p_ready[qt]);
+      TRACE(25);
       return true;
     };
 
-    for (int it = 0; it < nt; ++it) {
-      const int n0 = tile_of(it) * BN;
-      const int buf = it & 1;
-      if (!mbar_wait(&bars->s_full[buf], (it >> 1) & 1, abort_flag)) { alive = false; break; }
-      tc_fence_after();
-      const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= m0 + p.p_seq));
-      const bool ok = full_vis ? tile_body(std::false_type{}, it, n0, buf) : tile_body(std::true_type{}, it, n0, buf);
-      if (!ok) { alive = false; break; }
+    {
+      int cnt = 0;
+      for (int it = 0; it < nt; ++it) {
+        const int tk = tile_of(it);
+        if (tk >= my_nt) continue;
+        const int n0 = tk * BN;
+        TRACE(19);
+        if (!mbar_wait(&bars->s_full[qt], cnt & 1, abort_flag)) { alive = false; break; }
+        TRACE(20);
+        tc_fence_after();
+        const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= r_tile + p.p_seq));
+        const bool ok = full_vis ? tile_body(std::false_type{}, cnt, n0) : tile_body(std::true_type{}, cnt, n0);
+        if (!ok) { alive = false; break; }
+        ++cnt;
+      }
     }
     const float rs = rs_raw * scale;
+    TRACE_END();
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
-    if (alive && nt > 0) {
-      if (!mbar_wait(&bars->pv_done, (nt - 1) & 1, abort_flag)) alive = false;
+    if (alive && my_nt > 0) {
+      if (!mbar_wait(&bars->o_done, 0, abort_flag)) alive = false;
       tc_fence_after();
     }
-    if (alive) {
+    if (alive && r_tile < p.m_end) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh + (int64_t)i * p.o_ss;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        if (nt > 0) {
-          tmem_ld32(tmem_o + ((uint32_t)(lg * 32) << 16) + c * 32, r);
+        uint32_t ro[32];
+        if (my_nt > 0) {
+          tmem_ld32(t_o + c * 32, ro);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int x = 0; x < 32; ++x) r[x] = 0u;
+          for (int x = 0; x < 32; ++x) ro[x] = 0u;
         }
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 w;
-            w.x = pack2<T>(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
-            w.y = pack2<T>(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
-            w.z = pack2<T>(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
-            w.w = pack2<T>(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+            w.x = pack2<T>(__uint_as_float(ro[g * 8 + 0]) * inv, __uint_as_float(ro[g * 8 + 1]) * inv);
+            w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]) * inv, __uint_as_float(ro[g * 8 + 3]) * inv);
+            w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]) * inv, __uint_as_float(ro[g * 8 + 5]) * inv);
+            w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]) * inv, __uint_as_float(ro[g * 8 + 7]) * inv);
             *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
           }
         }
@@ -433,9 +518,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       if (row_ok) {
         if (p.L != nullptr)
           p.L[(int64_t)bh * p.M + i] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : FAWS_NEG_INF;
-        if (p.row_sum != nullptr) p.row_sum[(int64_t)bh * p.M + i] = rs;
+        if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs;
       }
-      if (store_scores && nt * BN < p.N) {
+      if constexpr (store_scores) if (my_nt * BN < p.N) {
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
         const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
@@ -444,8 +529,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          const int r0 = m0 + lg * 32 - p.m_begin;
-          for (int j0 = nt * BN; j0 < p.N; j0 += 32) tma_store_3d(&maps.st, stage, j0, r0, bh);
+          const int r0 = r_tile + lg * 32 - p.m_begin;
+          for (int j0 = my_nt * BN; j0 < p.N; j0 += 32) tma_store_3d(&maps.st, stage, j0, r0, bh);
           tma_store_commit();
         }
       }
@@ -551,20 +636,30 @@ int* device_status_word() {
   return words[dev];
 }
 
-template <typename T, int D>
-cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
+template <typename T, int D, int HOOK>
+cudaError_t launch_fwd_h(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
   using L = Smem<D>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
+    cudaError_t e =
+        cudaFuncSetAttribute(tc_fwd_kernel<T, D, HOOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const int nqb = (p.m_end + BM - 1) / BM - p.m_begin / BM;
-  dim3 grid(nqb, p.Hq, p.B);
-  tc_fwd_kernel<T, D><<<grid, NTHREADS, L::alloc, s>>>(maps, p, device_status_word());
+  const int ncb = (p.m_end - p.m_begin + CTA_ROWS - 1) / CTA_ROWS;
+  dim3 grid(ncb, p.Hq, p.B);
+  tc_fwd_kernel<T, D, HOOK><<<grid, NTHREADS, L::alloc, s>>>(maps, p, device_status_word());
   count_launch();
   return cudaGetLastError();
+}
+
+template <typename T, int D>
+cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
+  if (p.scores != nullptr) return launch_fwd_h<T, D, kHookScores>(maps, p, s);
+  if (p.row_sum != nullptr) return launch_fwd_h<T, D, kHookRowSum>(maps, p, s);
+  if (p.col_partial != nullptr) return launch_fwd_h<T, D, kHookColPart>(maps, p, s);
+  if (p.s_scratch != nullptr) return launch_fwd_h<T, D, kHookScratch>(maps, p, s);
+  return launch_fwd_h<T, D, kHookNone>(maps, p, s);
 }
 
 }  // namespace
@@ -612,6 +707,12 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
     return p.D == 128 ? launch_fwd_t<__half, 128>(maps, p, s) : launch_fwd_t<__half, 64>(maps, p, s);
   return p.D == 128 ? launch_fwd_t<__nv_bfloat16, 128>(maps, p, s) : launch_fwd_t<__nv_bfloat16, 64>(maps, p, s);
 }
+
+#ifdef FAWS_TRACE
+extern "C" int faws_debug_read_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
+}
+#endif
 
 int tc_read_status(int reset) {
   int* word = device_status_word();
