@@ -85,11 +85,24 @@ int run_fwd(const faws_problem* p, FwdParams& f, cudaStream_t s, int* block_m, i
   return FAWS_OK;
 }
 
-int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, cudaStream_t s) {
+// Key-major pass.  `final_out` receives (B,Hk,n_end) when group_sum != 0, else (B,Hq,n_end);
+// `per_head_ws` is scratch for the per-head sums when the CUDA-core kernel has to be followed
+// by a group sum.
+int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, float* final_out, float* per_head_ws,
+                   int group_sum, cudaStream_t s) {
   bool use_tc = false;
   if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_colsoftmax_supported(c, p->dtype);
-  if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
-  cudaError_t e = use_tc ? launch_tc_colsoftmax(c, p->dtype, s) : launch_generic_colsoftmax(c, p->dtype, s);
+  if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc && c.s_scratch == nullptr) return FAWS_EBACKEND;
+  cudaError_t e;
+  if (use_tc) {
+    c.out = final_out;
+    e = launch_tc_colsoftmax(c, p->dtype, group_sum, s);
+  } else {
+    const bool direct = !group_sum || c.G == 1;
+    c.out = direct ? final_out : per_head_ws;
+    e = launch_generic_colsoftmax(c, p->dtype, s);
+    if (e == cudaSuccess && !direct) e = launch_group_sum(per_head_ws, final_out, c.B, c.Hk, c.G, c.n_end, s);
+  }
   if (e != cudaSuccess) {
     std::fprintf(stderr, "faws: column-softmax launch failed: %s\n", cudaGetErrorString(e));
     return FAWS_ECUDA;
@@ -172,9 +185,7 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   int bm = 0, bn = 0;
   st = run_fwd(p, f, s, &bm, &bn);
   if (st != FAWS_OK) return st;
-  const int G = p->Hq / p->Hk;
-  const bool direct = per_q_head || G == 1;
-  ColSoftmaxParams c = make_cs(p, f.L, direct ? sum_out : w.per_head, i_begin, n_end);
+  ColSoftmaxParams c = make_cs(p, f.L, sum_out, i_begin, n_end);
   if (w.scratch != nullptr) { c.s_scratch = w.scratch; c.split = buffered_split; }
   if (i_begin >= p->m_end) {
     // no query of the window lies beyond the split: the sums are zero
@@ -182,11 +193,7 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
       return FAWS_ECUDA;
     return FAWS_OK;
   }
-  st = run_colsoftmax(p, c, s);
-  if (st != FAWS_OK) return st;
-  if (!direct && launch_group_sum(w.per_head, sum_out, p->B, p->Hk, G, n_end, s) != cudaSuccess)
-    return FAWS_ECUDA;
-  return FAWS_OK;
+  return run_colsoftmax(p, c, sum_out, w.per_head, per_q_head ? 0 : 1, s);
 }
 
 }  // namespace
@@ -277,7 +284,7 @@ int faws_total_attention(const faws_problem* p, float* total, void* stream) {
   if (st != FAWS_OK) return st;
   if (total == nullptr || p->log_normalizer == nullptr) return FAWS_EINVAL;
   ColSoftmaxParams c = make_cs(p, p->log_normalizer, total, 0, p->N);
-  return run_colsoftmax(p, c, static_cast<cudaStream_t>(stream));
+  return run_colsoftmax(p, c, total, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split) {

@@ -553,6 +553,226 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   }
 }
 
+// ---------------------------------------------------------------------------- key-major pass
+// Softmax column sums from a saved log-normaliser (the structure of total.py:50-142 and of the
+// reference's second passes, attention_with_col_softmax_sum.py:195-270,
+// attention_cross_token_softmax_sum.py:203-268, without atomics):
+//   out[j] = sum over heads of the CTA and queries i of exp(s_ij - L_i).
+// One CTA owns 128 keys of one (batch, kv head or query head) and walks the query tiles of its
+// heads.  S^T = K.Q^T puts keys on TMEM lanes, so thread j accumulates column j in a register:
+// no cross-thread reduction, fixed order, one store.  Four S^T buffers; the two consumer
+// warpgroups take alternate query tiles and are added in a fixed order at the end.
+constexpr int CS_QSLOTS = 4;
+
+template <int D>
+struct CsSmem {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kSub = 128 * 128;
+  static constexpr int k_off = 0;
+  static constexpr int q_off = k_off + kTile;
+  static constexpr int l_off = q_off + CS_QSLOTS * kTile;  // [4][128] floats: -L_i*log2e per query
+  static constexpr int comb_off = l_off + 4 * 128 * 4;     // [128] floats
+  static constexpr int bar_off = comb_off + 128 * 4;
+  static constexpr int total = bar_off + 256;
+  static constexpr int alloc = total + 1024;
+};
+
+struct CsBars {
+  uint64_t k_full;
+  uint64_t q_full[CS_QSLOTS], q_empty[CS_QSLOTS];
+  uint64_t s_full[4], s_free[4];
+  uint64_t l_ready[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct CsMaps {
+  CUtensorMap q, k;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(NTHREADS, 1)
+tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams p, int heads_per_cta,
+                     int* __restrict__ status) {
+  using L = CsSmem<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  CsBars* bars = reinterpret_cast<CsBars*>(smem + L::bar_off);
+  volatile int* abort_flag = &bars->abort_flag;
+  float* lbuf = reinterpret_cast<float*>(smem + L::l_off);
+  float* comb = reinterpret_cast<float*>(smem + L::comb_off);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int ho = blockIdx.y, b = blockIdx.z;
+  const int h0 = ho * heads_per_cta;  // first query head of this CTA
+  const int hk = h0 / p.G;
+
+  // query tiles (absolute multiples of 128) this key tile needs, per head
+  const int i_lo = max(p.i_begin, p.m_begin);
+  int i_first = i_lo;
+  if (p.causal) i_first = max(i_first, n0 - p.p_seq);
+  const int qt0 = i_first / BM;
+  const int ntq = max(0, (p.m_end + BM - 1) / BM - qt0);
+  const int total = ntq * heads_per_cta;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->k_full, 1);
+    for (int s = 0; s < CS_QSLOTS; ++s) {
+      mbar_init(&bars->q_full[s], 1);
+      mbar_init(&bars->q_empty[s], 1);
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->s_free[s], 128);
+    }
+    mbar_init(&bars->l_ready[0], 128);
+    mbar_init(&bars->l_ready[1], 128);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&maps.q);
+    prefetch_tmap(&maps.k);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  float acc = 0.f;
+  if (warp < 4) {
+    reg_dealloc<REGS_AUX>();
+    if (warp == 0 && lane == 0 && total > 0) {
+      // ---------------------------------------------------------- TMA producer
+      mbar_arrive_expect_tx(&bars->k_full, L::kTile);
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_4d(smem + L::k_off + c * L::kSub, &maps.k, &bars->k_full, c * 64, n0, hk, b);
+      for (int u = 0; u < total; ++u) {
+        const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
+        const int g = u / ntq, qt = qt0 + (u - g * ntq);
+        if (!mbar_wait(&bars->q_empty[s], (use & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(&bars->q_full[s], L::kTile);
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::q_off + s * L::kTile + c * L::kSub, &maps.q, &bars->q_full[s], c * 64, qt * BM,
+                      h0 + g, b);
+      }
+    } else if (warp == 1 && lane == 0 && total > 0) {
+      // ---------------------------------------------------------- MMA issuer: S^T = K . Q^T
+      constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
+      constexpr uint32_t idesc = make_idesc_f16(128, BM, kFmt, 0, 0);
+      const uint32_t k_addr = smem_u32(smem + L::k_off);
+      bool ok = mbar_wait(&bars->k_full, 0, abort_flag);
+      for (int u = 0; ok && u < total; ++u) {
+        const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
+        if (!(ok = mbar_wait(&bars->q_full[s], use & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(&bars->s_free[s], (use & 1) ^ 1, abort_flag))) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(smem + L::q_off + s * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
+          mma_ss(tmem_base + (uint32_t)(s * BM), make_desc_sw128(k_addr + off, 16, 1024),
+                 make_desc_sw128(q_addr + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&bars->q_empty[s]);
+        mma_commit(&bars->s_full[s]);
+      }
+    }
+  } else {
+    reg_alloc<REGS_SOFTMAX>();
+    // ------------------------------------------------------------ consumers: thread = key
+    const int wg = (warp - 4) >> 2;
+    const int lg = warp & 3;
+    const int row = lg * 32 + lane;
+    const int j = n0 + row;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
+    const float scale_log2 = p.sm_scale * kLog2e;
+
+    // -L_i*log2e of query tile u (for this thread's column x = row), -inf where the query is
+    // outside the summed range or has no visible key
+    auto load_negl = [&](int u) -> float {
+      const int g = u / ntq, qt = qt0 + (u - g * ntq);
+      const int i = qt * BM + row;
+      float v = FAWS_NEG_INF;
+      if (i >= i_lo && i < p.m_end) {
+        const float Li = p.L[((int64_t)b * p.Hq + h0 + g) * p.M + i];
+        if (Li != FAWS_NEG_INF) v = -Li * kLog2e;
+      }
+      return v;
+    };
+
+    bool alive = true;
+    int mine = 0;  // tiles this warpgroup has processed
+    float negl_next = (wg < total) ? load_negl(wg) : FAWS_NEG_INF;
+    for (int u = wg; u < total; u += 2, ++mine) {
+      const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
+      float* lb = lbuf + s * 128;
+      lb[row] = negl_next;  // slot s was last read by this warpgroup two tiles ago (before its l_ready wait)
+      mbar_arrive(&bars->l_ready[wg]);
+      if (u + 2 < total) negl_next = load_negl(u + 2);
+      if (!mbar_wait(&bars->l_ready[wg], mine & 1, abort_flag)) { alive = false; break; }
+      if (!mbar_wait(&bars->s_full[s], use & 1, abort_flag)) { alive = false; break; }
+      tc_fence_after();
+      uint32_t r[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        tmem_ld32(t_lane + (uint32_t)(s * BM) + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&bars->s_free[s]);
+
+      const int g = u / ntq, qt = qt0 + (u - g * ntq);
+      const int i0 = qt * BM;
+      // causal: query column x is visible to key j iff i0 + x + p_seq >= j
+      const int xlo = p.causal ? (j - p.p_seq - i0) : 0;
+      const bool full = !p.causal || (n0 + BN - 1 - p.p_seq - i0 <= 0);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      if (full) {
+#pragma unroll
+        for (int x = 0; x < 128; x += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(lb + x);
+          a0 += fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x));
+          a1 += fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y));
+          a2 += fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z));
+          a3 += fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w));
+        }
+      } else {
+#pragma unroll
+        for (int x = 0; x < 128; x += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(lb + x);
+          a0 += (x >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x)) : 0.f;
+          a1 += (x + 1 >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y)) : 0.f;
+          a2 += (x + 2 >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z)) : 0.f;
+          a3 += (x + 3 >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w)) : 0.f;
+        }
+      }
+      acc += (a0 + a1) + (a2 + a3);
+    }
+    if (!alive) acc = 0.f;
+    if (wg == 1) comb[row] = acc;
+  }
+
+  // ------------------------------------------------------------ common exit
+  tc_fence_before();
+  __syncthreads();
+  if (warp >= 4 && warp < 8) {
+    const int row = (warp & 3) * 32 + lane;
+    const int j = n0 + row;
+    if (j < p.n_end) p.out[((int64_t)b * gridDim.y + ho) * p.n_end + j] = acc + comb[row];
+  }
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
+    for (int w = 0; w < 50; ++w) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -723,7 +943,46 @@ int tc_read_status(int reset) {
   return v;
 }
 
-bool tc_colsoftmax_supported(const ColSoftmaxParams&, int) { return false; }
-cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams&, int, cudaStream_t) { return cudaErrorNotSupported; }
+bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype) {
+  (void)dtype;
+  if (p.D != 64 && p.D != 128) return false;
+  if (p.s_scratch != nullptr) return false;  // the buffered pass reads stored scores, no MMA
+  if (p.m_begin % BM != 0 || !(p.sm_scale > 0.f)) return false;
+  if (!device_is_sm100() || get_encode() == nullptr) return false;
+  if (!ok16(p.q, p.q_sb, p.q_sh, p.q_ss) || !ok16(p.k, p.k_sb, p.k_sh, p.k_ss)) return false;
+  return p.n_end > 0;
+}
+
+namespace {
+template <typename T, int D>
+cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads_per_cta, cudaStream_t s) {
+  using L = CsSmem<D>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e =
+        cudaFuncSetAttribute(tc_colsoftmax_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  dim3 grid((p.n_end + BN - 1) / BN, p.Hq / heads_per_cta, p.B);
+  tc_colsoftmax_kernel<T, D><<<grid, NTHREADS, L::alloc, s>>>(maps, p, heads_per_cta, device_status_word());
+  count_launch();
+  return cudaGetLastError();
+}
+}  // namespace
+
+// group_sum != 0: one CTA walks the G query heads of a kv head and p.out is (B,Hk,n_end);
+// otherwise one CTA per query head and p.out is (B,Hq,n_end).
+cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, int group_sum, cudaStream_t s) {
+  CsMaps maps;
+  if (!make_map_bhsd(&maps.q, p.q, p.D, p.m_end, p.Hq, p.B, p.q_ss, p.q_sh, p.q_sb, 128) ||
+      !make_map_bhsd(&maps.k, p.k, p.D, p.N, p.Hk, p.B, p.k_ss, p.k_sh, p.k_sb, 128))
+    return cudaErrorInvalidValue;
+  const int hpc = group_sum ? p.G : 1;
+  if (dtype == FAWS_FP16)
+    return p.D == 128 ? launch_cs_t<__half, 128>(maps, p, hpc, s) : launch_cs_t<__half, 64>(maps, p, hpc, s);
+  return p.D == 128 ? launch_cs_t<__nv_bfloat16, 128>(maps, p, hpc, s)
+                    : launch_cs_t<__nv_bfloat16, 64>(maps, p, hpc, s);
+}
 
 }  // namespace faws
