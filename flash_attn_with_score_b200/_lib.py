@@ -11,6 +11,8 @@ LIB_PATH = os.path.join(HERE, "libfaws.so")
 FP16, BF16 = 0, 1
 SCORES_F32, SCORES_INPUT = 0, 1
 BACKEND_AUTO, BACKEND_GENERIC, BACKEND_TCGEN05 = 0, 1, 2
+ETOOLARGE = -6
+NOALLOC_SCRATCH_BYTES = 8 << 20
 BACKENDS = {None: BACKEND_AUTO, "auto": BACKEND_AUTO, "generic": BACKEND_GENERIC, "tcgen05": BACKEND_TCGEN05}
 
 OP_ATTENTION, OP_SCORES, OP_ROW_SUM, OP_COL_SUM, OP_COL_SUM_SEQUENTIAL = 0, 1, 2, 3, 4
@@ -20,7 +22,8 @@ OP_TOTAL_ATTENTION = 9
 # every symbol include/faws.h declares
 EXPORTS = [
     "faws_attention", "faws_attention_with_scores", "faws_attention_with_row_sum",
-    "faws_attention_with_col_sum", "faws_attention_with_col_sum_sequential",
+    "faws_attention_with_col_sum", "faws_attention_with_col_sum_noalloc",
+    "faws_attention_with_col_sum_sequential",
     "faws_attention_with_softmax_col_sum", "faws_attention_cross_token_qk_sum",
     "faws_attention_cross_token_softmax_sum", "faws_attention_cross_token_softmax_sum_buffered",
     "faws_total_attention", "faws_workspace_bytes", "faws_reduce_ranks", "faws_device_status", "faws_last_backend",
@@ -63,6 +66,7 @@ def load():
         "faws_attention_with_scores": (i32, [PP, vp, i32, u32, vp]),
         "faws_attention_with_row_sum": (i32, [PP, vp, vp]),
         "faws_attention_with_col_sum": (i32, [PP, vp, i32, vp, sz, vp]),
+        "faws_attention_with_col_sum_noalloc": (i32, [PP, vp, i32, vp]),
         "faws_attention_with_col_sum_sequential": (i32, [PP, vp, i32, vp, sz, vp]),
         "faws_attention_with_softmax_col_sum": (i32, [PP, vp, i32, vp, sz, vp]),
         "faws_attention_cross_token_qk_sum": (i32, [PP, i32, vp, i32, vp, sz, vp]),

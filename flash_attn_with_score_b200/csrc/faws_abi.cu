@@ -329,6 +329,7 @@ const char* faws_strerror(int status) {
     case FAWS_EWORKSPACE: return "workspace missing or too small";
     case FAWS_ECUDA: return "CUDA call failed";
     case FAWS_EBACKEND: return "requested kernel family cannot run this problem";
+    case FAWS_ETOOLARGE: return "problem needs more scratch than the built-in array of the _noalloc entry point";
     default: return "unknown status";
   }
 }

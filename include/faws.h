@@ -43,6 +43,8 @@ extern "C" {
 #define FAWS_EWORKSPACE (-3)  /* workspace missing or too small               */
 #define FAWS_ECUDA (-4)       /* a CUDA runtime / driver call failed          */
 #define FAWS_EBACKEND (-5)    /* forced backend cannot run this problem       */
+#define FAWS_ETOOLARGE (-6)   /* problem exceeds the built-in scratch of the  */
+                              /* _noalloc entry point                         */
 
 /* kernel families ("backend" below) */
 #define FAWS_BACKEND_AUTO 0    /* tcgen05 kernels when the problem fits them   */
@@ -127,6 +129,26 @@ int faws_attention_with_row_sum(const faws_problem* p, float* row_sum, void* str
  */
 int faws_attention_with_col_sum(const faws_problem* p, float* col_sum, int32_t per_q_head,
                                 void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * faws_attention_with_col_sum for callers that cannot supply a workspace: a host whose own
+ * pool allocator owns the device and forbids cudaMalloc in plugins, a serving loop that
+ * cannot afford the device-wide synchronisation of cudaMalloc/cudaFree, a plugin interface
+ * that hands over tensor pointers only.  Same arguments and results as
+ * faws_attention_with_col_sum minus the workspace; the per-query-tile partial sums go to a
+ * fixed FAWS_NOALLOC_SCRATCH_BYTES array inside the library (held on every GPU that loads
+ * the library until the process exits).  It has no counterpart in the reference.
+ *  - Returns FAWS_ETOOLARGE when faws_workspace_bytes(FAWS_OP_COL_SUM, p, 0) exceeds
+ *    FAWS_NOALLOC_SCRATCH_BYTES.
+ *  - Calls no cudaMalloc / cudaFree / allocating routine.  The first call on a device
+ *    resolves the array's address once; make it before any stream capture.
+ *  - All calls on a device share the array: calls whose kernels may overlap on the GPU
+ *    race; order them on one stream or with events.  Nothing needs to be zeroed between
+ *    calls (each call writes every partial it later reads).
+ */
+#define FAWS_NOALLOC_SCRATCH_BYTES (8u << 20)
+int faws_attention_with_col_sum_noalloc(const faws_problem* p, float* col_sum, int32_t per_q_head,
+                                        void* stream);
 
 /* Replaces attention_with_col_sum_sequential
  * (attention_with_col_sum_sequential.py:214-341): round-robin key-tile order
