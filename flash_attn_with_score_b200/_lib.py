@@ -6,7 +6,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libfaws.so")
+LIB_PATH = os.environ.get("FAWS_LIB_PATH") or os.path.join(HERE, "libfaws.so")  # override: ablation builds
 
 FP16, BF16 = 0, 1
 SCORES_F32, SCORES_INPUT = 0, 1

@@ -11,7 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "libfaws.so")
+LIB = os.environ.get("FAWS_LIB_PATH") or os.path.join(HERE, "libfaws.so")
 SOURCES = ["faws_abi.cu", "faws_generic.cu", "faws_tc.cu", "faws_noalloc.cu"]
 HEADERS = ["faws_internal.cuh", "faws_tc_ptx.cuh"]
 

@@ -67,7 +67,8 @@ __device__ long long g_trace[3 * 4096];
 #endif
 
 struct TcMaps {
-  CUtensorMap q, k, v, st;  // st: scores (or score-scratch) store map
+  CUtensorMap q, k, v, o;  // o: 32-row store boxes of the output
+  CUtensorMap st;          // scores (or score-scratch) store map
 };
 
 template <int D>
@@ -125,6 +126,9 @@ template <typename T, int D, int HOOK>
 __global__ void __launch_bounds__(NTHREADS, 1)
 tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __restrict__ status) {
   using L = Smem<D>;
+#ifdef FAWS_TRACE
+  const long long t_entry = clock64();
+#endif
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -153,6 +157,22 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   }
   const int nt = max(nt_q[0], nt_q[1]);
 
+  auto tile_of = [&](int it) -> int {
+    if (p.schedule == kReverse) return nt - 1 - it;
+    if (p.schedule == kRoundRobin) return (cb_abs + it) % nt;
+    return it;
+  };
+  // K(0), V(0), K(1), V(1), ... go through the ring in this order
+  auto issue_kv_load = [&](int idx) {
+    const int s = idx % KV_SLOTS;
+    const int n0 = tile_of(idx >> 1) * BN;
+    mbar_arrive_expect_tx(&bars->kv_full[s], L::kTile);
+    const CUtensorMap* map = (idx & 1) ? &maps.v : &maps.k;
+    for (int c = 0; c < D / 64; ++c)
+      tma_load_4d(smem + L::kv_off + s * L::kTile + c * L::kSub, map, &bars->kv_full[s], c * 64, n0, hk, b);
+  };
+  const int n_early = min(KV_SLOTS, 2 * nt);  // loads issued before the CTA-wide set-up barrier
+
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < KV_SLOTS; ++s) {
@@ -167,9 +187,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     mbar_init(&bars->o_done, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
-    prefetch_tmap(&maps.q);
-    prefetch_tmap(&maps.k);
-    prefetch_tmap(&maps.v);
+    // This thread is also the TMA producer: start the first loads now so that their HBM
+    // latency overlaps the TMEM allocation and the set-up barrier.
+    if (nt > 0) {
+      mbar_arrive_expect_tx(&bars->q_full, 2 * L::kTile);
+      for (int t = 0; t < 2; ++t)
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
+                      m0 - p.m_begin + t * BM, h, b);
+      for (int idx = 0; idx < n_early; ++idx) issue_kv_load(idx);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, TMEM_COLS);
@@ -180,29 +207,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  auto tile_of = [&](int it) -> int {
-    if (p.schedule == kReverse) return nt - 1 - it;
-    if (p.schedule == kRoundRobin) return (cb_abs + it) % nt;
-    return it;
-  };
-
   if (warp < 4) {
     reg_dealloc<REGS_AUX>();
     if (warp == 0 && lane == 0) {
-      // ---------------------------------------------------------- TMA producer
-      mbar_arrive_expect_tx(&bars->q_full, 2 * L::kTile);
-      for (int t = 0; t < 2; ++t)
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
-                      m0 - p.m_begin + t * BM, h, b);
-      for (int idx = 0; idx < 2 * nt; ++idx) {  // K(0), V(0), K(1), V(1), ...
+      // ---------------------------------------------------------- TMA producer (rest of the ring)
+      for (int idx = n_early; idx < 2 * nt; ++idx) {
         const int s = idx % KV_SLOTS, u = idx / KV_SLOTS;
-        const int n0 = tile_of(idx >> 1) * BN;
         if (!mbar_wait(&bars->kv_empty[s], (u & 1) ^ 1, abort_flag)) break;
-        mbar_arrive_expect_tx(&bars->kv_full[s], L::kTile);
-        const CUtensorMap* map = (idx & 1) ? &maps.v : &maps.k;
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::kv_off + s * L::kTile + c * L::kSub, map, &bars->kv_full[s], c * 64, n0, hk, b);
+        issue_kv_load(idx);
       }
     } else if (warp == 1 && lane == 0 && nt > 0) {
       // ---------------------------------------------------------- MMA issuer
@@ -314,10 +326,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0);
     int tr_n = 0;
     long long* tr_buf = g_trace + qt * 4096;
+    if (tr_on) { tr_buf[0] = 99; tr_buf[1] = t_entry; tr_n = 1; }
+    TRACE(1);
 #endif
 
-    // One key tile.  The row's 128 scores are read from TMEM once and stay in registers for
-    // both passes.  kMasked = false is the common case of a fully visible tile.
+    // One key tile.  The row's 128 scores are read from TMEM once and stay in registers: first
+    // for the max and exp2 passes (the chain the tensor pipe waits on), then, after P has been
+    // handed back, for the score-tile hook.  kMasked = false is the fully visible tile.
     auto tile_body = [&](auto masked_tag, int cnt, int n0) -> bool {
       constexpr bool kMasked = decltype(masked_tag)::value;
       uint32_t r[128];
@@ -333,7 +348,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
 #define FAWS_VIS(x) (!kMasked || (x) < nvis)
 
-      // ---- pass 1: row max (4 independent chains) and the score-tile hooks
+      // ---- row max (4 independent chains)
       float a0 = FAWS_NEG_INF, a1 = FAWS_NEG_INF, a2 = FAWS_NEG_INF, a3 = FAWS_NEG_INF;
 #pragma unroll
       for (int x = 0; x < 128; x += 4) {
@@ -343,7 +358,65 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         a3 = fmaxf(a3, FAWS_VIS(x + 3) ? __uint_as_float(r[x + 3]) : FAWS_NEG_INF);
       }
       const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * scale_log2;  // sm_scale > 0
+      TRACE(22);
 
+      // ---- running max, lazy rescale of O.  s_full for this tile was committed after this
+      // query tile's previous P.V MMA, so O_t is quiescent here.
+      const float m_new = fmaxf(m_run, mx);
+      const bool need = m_new > m_run + kRescaleThreshold;
+      float alpha = 1.f;
+      if (need) {
+        alpha = fast_exp2(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+      }
+      if (cnt > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ro[32];
+          tmem_ld32(t_o + c * 32, ro);
+          tmem_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
+          tmem_st32(t_o + c * 32, ro);
+        }
+      }
+      TRACE(23);
+
+      // ---- P = exp2(s*scale*log2e - m), row sum of P, P -> TMEM over S as 16-bit pairs
+      const float neg_m = (m_run == FAWS_NEG_INF) ? 0.f : -m_run;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float e[8];
+#pragma unroll
+          for (int y = 0; y < 8; ++y) {
+            const int x = c * 32 + g * 8 + y;
+            const float pe = fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, neg_m));
+            e[y] = FAWS_VIS(x) ? pe : 0.f;
+          }
+          l0 += e[0] + e[4];
+          l1 += e[1] + e[5];
+          l2 += e[2] + e[6];
+          l3 += e[3] + e[7];
+          pk[g * 4 + 0] = pack2<T>(e[0], e[1]);
+          pk[g * 4 + 1] = pack2<T>(e[2], e[3]);
+          pk[g * 4 + 2] = pack2<T>(e[4], e[5]);
+          pk[g * 4 + 3] = pack2<T>(e[6], e[7]);
+        }
+        tmem_st16(t_s + c * 16, pk);
+      }
+      TRACE(24);
+      tmem_wait_st();
+      l_run += (l0 + l1) + (l2 + l3);
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready[qt]);
+      TRACE(25);
+
+      // ---- score-tile hooks: off the chain above, they overlap this tile's P.V MMA
       if constexpr (HOOK == kHookRowSum) {
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
@@ -367,12 +440,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 #pragma unroll
             for (int cc = 0; cc < 8; ++cc) {
               float4 val;
-              float* vp = reinterpret_cast<float*>(&val);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int x = c * 32 + cc * 4 + e;
-                const float sc = __uint_as_float(r[x]) * scale;
-                vp[e] = (store_scratch || FAWS_VIS(x)) ? sc : masked_f;
+              val.x = __uint_as_float(r[c * 32 + cc * 4 + 0]) * scale;
+              val.y = __uint_as_float(r[c * 32 + cc * 4 + 1]) * scale;
+              val.z = __uint_as_float(r[c * 32 + cc * 4 + 2]) * scale;
+              val.w = __uint_as_float(r[c * 32 + cc * 4 + 3]) * scale;
+              if (kMasked && store_scores) {
+                if (!(c * 32 + cc * 4 + 0 < nvis)) val.x = masked_f;
+                if (!(c * 32 + cc * 4 + 1 < nvis)) val.y = masked_f;
+                if (!(c * 32 + cc * 4 + 2 < nvis)) val.z = masked_f;
+                if (!(c * 32 + cc * 4 + 3 < nvis)) val.w = masked_f;
               }
               *reinterpret_cast<float4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = val;
             }
@@ -408,61 +484,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           p.col_partial[((int64_t)bh * p.n_qb_part + (qb128 - p.qb_first)) * (int64_t)p.ncols_pad + n0 + row] = sum;
         }
       }
-
-      // ---- running max, lazy rescale of O.  s_full for this tile was committed after this
-      // query tile's previous P.V MMA, so O_t is quiescent here.
-      TRACE(22);
-      const float m_new = fmaxf(m_run, mx);
-      const bool need = m_new > m_run + kRescaleThreshold;
-      float alpha = 1.f;
-      if (need) {
-        alpha = fast_exp2(m_run - m_new);
-        m_run = m_new;
-        l_run *= alpha;
-      }
-      if (cnt > 0 && __any_sync(0xffffffffu, need)) {
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t ro[32];
-          tmem_ld32(t_o + c * 32, ro);
-          tmem_wait_ld();
-#pragma unroll
-          for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * alpha);
-          tmem_st32(t_o + c * 32, ro);
-        }
-      }
-
-      TRACE(23);
-      // ---- pass 2: P = exp2(s*scale*log2e - m), row sum of P, P -> TMEM over S (16-bit pairs)
-      const float neg_m = (m_run == FAWS_NEG_INF) ? 0.f : -m_run;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        float e[8];
-#pragma unroll
-        for (int y = 0; y < 8; ++y) {
-          const int x = g * 8 + y;
-          const float pe = fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, neg_m));
-          e[y] = FAWS_VIS(x) ? pe : 0.f;
-        }
-        l0 += e[0] + e[4];
-        l1 += e[1] + e[5];
-        l2 += e[2] + e[6];
-        l3 += e[3] + e[7];
-        r[g * 4 + 0] = pack2<T>(e[0], e[1]);
-        r[g * 4 + 1] = pack2<T>(e[2], e[3]);
-        r[g * 4 + 2] = pack2<T>(e[4], e[5]);
-        r[g * 4 + 3] = pack2<T>(e[6], e[7]);
-      }
-      tmem_st32(t_s, reinterpret_cast<const uint32_t(&)[32]>(r[0]));
-      tmem_st32(t_s + 32, reinterpret_cast<const uint32_t(&)[32]>(r[32]));
-      TRACE(24);
-      tmem_wait_st();
-      l_run += (l0 + l1) + (l2 + l3);
 #undef FAWS_VIS
-      tc_fence_before();
-      mbar_arrive(&bars->p_ready[qt]);
-      TRACE(25);
+      TRACE(26);
       return true;
     };
 
@@ -483,27 +506,24 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
     }
     const float rs = rs_raw * scale;
-    TRACE_END();
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
     if (alive && my_nt > 0) {
       if (!mbar_wait(&bars->o_done, 0, abort_flag)) alive = false;
       tc_fence_after();
     }
+    TRACE(30);
     if (alive && r_tile < p.m_end) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh + (int64_t)i * p.o_ss;
+      if (my_nt > 0) {
+        // Every MMA of the CTA has completed, so the Q tiles' shared memory is free: each warp
+        // stages its 32 x D output block there (128B-swizzled) and stores it with TMA.
+        unsigned char* ost = smem + L::q_off + (warp - 4) * (32 * D * 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t ro[32];
-        if (my_nt > 0) {
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ro[32];
           tmem_ld32(t_o + c * 32, ro);
           tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int x = 0; x < 32; ++x) ro[x] = 0u;
-        }
-        if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 w;
@@ -511,9 +531,23 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
             w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]) * inv, __uint_as_float(ro[g * 8 + 3]) * inv);
             w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]) * inv, __uint_as_float(ro[g * 8 + 5]) * inv);
             w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]) * inv, __uint_as_float(ro[g * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+            const int cc = (c & 1) * 4 + g;  // 16-byte chunk inside the 64-column sub-tile
+            *reinterpret_cast<uint4*>(ost + (c >> 1) * 4096 + lane * 128 + ((cc ^ (lane & 7)) << 4)) = w;
           }
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          for (int sub = 0; sub < D / 64; ++sub)
+            tma_store_4d(&maps.o, ost + sub * 4096, sub * 64, r_tile + lg * 32 - p.m_begin, h, b);
+          tma_store_commit();
+        }
+      } else if (row_ok) {
+        // no key is visible to this query tile: its rows are zero
+        T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh + (int64_t)i * p.o_ss;
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int g = 0; g < D / 8; ++g) *reinterpret_cast<uint4*>(orow + g * 8) = z;
       }
       if (row_ok) {
         if (p.L != nullptr)
@@ -535,7 +569,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         }
       }
     }
+    TRACE(31);
     if (lane == 0) tma_store_wait<0>();
+    TRACE(32);
+    TRACE_END();
   }
 
   // ------------------------------------------------------------ common exit
@@ -911,6 +948,8 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
       !make_map_bhsd(&maps.k, p.k, p.D, p.N, p.Hk, p.B, p.k_ss, p.k_sh, p.k_sb, 128) ||
       !make_map_bhsd(&maps.v, p.v, p.D, p.N, p.Hk, p.B, p.v_ss, p.v_sh, p.v_sb, 128))
     return cudaErrorInvalidValue;
+  const char* obase = static_cast<const char*>(p.o) + (int64_t)p.m_begin * p.o_ss * 2;
+  if (!make_map_bhsd(&maps.o, obase, p.D, q_rows, p.Hq, p.B, p.o_ss, p.o_sh, p.o_sb, 32)) return cudaErrorInvalidValue;
   maps.st = maps.q;
   if (p.scores != nullptr) {
     float* base = static_cast<float*>(p.scores) + (int64_t)p.m_begin * p.N;
