@@ -36,6 +36,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CFG2 = dict(B=1, Hq=32, Hk=32, S=1024, D=128, dtype=torch.float16, causal=True)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on this
+# workload, from the ncu capture summarised in profiles/tc_fwd_scores_cfg2.md (None = not captured)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 111_794_688  # 25.32 MB read + 86.47 MB written (the rest stays dirty in L2)
 N_SETS = 4  # rotating buffer sets: 4 x (134 MB scores + 8 MB out + 25 MB inputs) > 126 MB of L2
 
 
@@ -309,8 +312,21 @@ def main():
     launches = F.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_start.elapsed_time(t_end)
-    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    step_event_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
     status = F.device_status()
+
+    # Duration of the kernel itself: the same launches with the stream kept busy (a spin kernel
+    # is queued first so the host runs ahead), so that the event pairs bracket the launch and
+    # not the host's enqueue latency.
+    kev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    torch.cuda._sleep(int(4e6 + 1.2e5 * args.steps))
+    for i in range(args.steps):
+        kev[i][0].record()
+        step(i)
+        kev[i][1].record()
+    torch.cuda.synchronize()
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in kev)
 
     t = torch.tensor([total_ms, kern_ms], device=device, dtype=torch.float64)
     if world > 1:
@@ -367,17 +383,13 @@ def main():
         "roofline": {"bound": "hbm", "achieved": nbytes / (kern_ms * 1e-3) / 1e9, "peak": pk["hbm"],
                      "unit": "GB/s", "frac": nbytes / (kern_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
                      "peak_source": pk["src"], "kernel": "tc_fwd_kernel<half,128> (scores hook)",
-                     "algorithmic_bytes": nbytes, "kernel_ms": kern_ms},
+                     "algorithmic_bytes": nbytes, "kernel_ms": kern_ms, "step_event_ms": step_event_ms,
+                     "timing": "CUDA events around each launch on the launching stream, stream kept busy"},
         "e2e": {"value": world * score_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
         "gpu_launches": launches, "backend": F.last_backend(), "device_status": status, "clocks": clocks,
     }
-    traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_path):
-        try:
-            line["roofline"]["traffic"] = json.load(open(traffic_path)).get("cfg2_scores_bytes_per_launch")
-        except Exception:
-            pass
+    line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
     if world == 1 and not args.no_cpu:
         ts = cpu_reference_time(cfg, 5)
         sec = statistics.median(ts)
