@@ -221,8 +221,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
       constexpr uint32_t idesc_qk = make_idesc_f16(128, BN, kFmt, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + L::q_off);
-      const uint32_t kv_addr = smem_u32(smem + L::kv_off);
+      // Operand descriptors are built once; inside the loops only compile-time offsets (in
+      // 16-byte units) are added to their address field, so the issuing thread spends a few
+      // instructions per MMA.
+      const uint64_t q_desc0 = make_desc_sw128(smem_u32(smem + L::q_off), 16, 1024);
+      const uint64_t k_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), 16, 1024);
+      const uint64_t v_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), L::kSub, 1024);
       auto kv_wait = [&](int idx) -> bool {
         if (!mbar_wait(&bars->kv_full[idx % KV_SLOTS], (idx / KV_SLOTS) & 1, abort_flag)) return false;
         tc_fence_after();
@@ -230,24 +234,28 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       };
       // S_t = Q_t . K^T for the key tile in ring slot `slot`
       auto issue_qk = [&](int t, int slot) {
-        const uint32_t k_addr = kv_addr + (uint32_t)(slot * L::kTile);
-        const uint32_t qa = q_addr + (uint32_t)(t * L::kTile);
+        const uint64_t qd = q_desc0 + (uint64_t)(t * (L::kTile >> 4));
+        const uint64_t kd = k_desc0 + (uint64_t)(slot * (L::kTile >> 4));
+        const uint32_t d_tmem = tmem_base + (uint32_t)(t * BN);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
-          mma_ss(tmem_base + (uint32_t)(t * BN), make_desc_sw128(qa + off, 16, 1024),
-                 make_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
+          if (kk == 0) mma_ss(d_tmem, qd + off, kd + off, idesc_qk, 0u);
+          else mma_ss_acc(d_tmem, qd + off, kd + off, idesc_qk);
         }
         mma_commit(&bars->s_full[t]);
       };
       // O_t (+)= P_t . V; P_t sits in the first 64 columns of S_t (two 16-bit values per column)
       auto issue_pv = [&](int t, int slot, bool accumulate) {
-        const uint32_t v_addr = kv_addr + (uint32_t)(slot * L::kTile);
+        const uint64_t vd = v_desc0 + (uint64_t)(slot * (L::kTile >> 4));
+        const uint32_t d_tmem = tmem_base + 256 + (uint32_t)(t * BN);
+        const uint32_t a_tmem = tmem_base + (uint32_t)(t * BN);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          mma_ts(tmem_base + 256 + (uint32_t)(t * BN), tmem_base + (uint32_t)(t * BN) + (uint32_t)(kk * 8),
-                 make_desc_sw128(v_addr + (uint32_t)(kk * 16 * 128), L::kSub, 1024), idesc_pv,
-                 (accumulate || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t off = (uint64_t)((kk * 16 * 128) >> 4);
+          if (kk == 0) mma_ts(d_tmem, a_tmem, vd, idesc_pv, accumulate ? 1u : 0u);
+          else mma_ts_acc(d_tmem, a_tmem + (uint32_t)(kk * 8), vd + off, idesc_pv);
+        }
       };
       int cnt[2] = {0, 0};  // key tiles each query tile has been given so far
       TRACE_DECL(2)
@@ -699,19 +707,21 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       // ---------------------------------------------------------- MMA issuer: S^T = K . Q^T
       constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
       constexpr uint32_t idesc = make_idesc_f16(128, BM, kFmt, 0, 0);
-      const uint32_t k_addr = smem_u32(smem + L::k_off);
+      const uint64_t k_desc = make_desc_sw128(smem_u32(smem + L::k_off), 16, 1024);
+      const uint64_t q_desc0 = make_desc_sw128(smem_u32(smem + L::q_off), 16, 1024);
       bool ok = mbar_wait(&bars->k_full, 0, abort_flag);
       for (int u = 0; ok && u < total; ++u) {
         const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
         if (!(ok = mbar_wait(&bars->q_full[s], use & 1, abort_flag))) break;
         if (!(ok = mbar_wait(&bars->s_free[s], (use & 1) ^ 1, abort_flag))) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(smem + L::q_off + s * L::kTile);
+        const uint64_t qd = q_desc0 + (uint64_t)(s * (L::kTile >> 4));
+        const uint32_t d_tmem = tmem_base + (uint32_t)(s * BM);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (uint32_t)((kk >> 2) * L::kSub + (kk & 3) * 32);
-          mma_ss(tmem_base + (uint32_t)(s * BM), make_desc_sw128(k_addr + off, 16, 1024),
-                 make_desc_sw128(q_addr + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
+          if (kk == 0) mma_ss(d_tmem, k_desc + off, qd + off, idesc, 0u);
+          else mma_ss_acc(d_tmem, k_desc + off, qd + off, idesc);
         }
         mma_commit(&bars->q_empty[s]);
         mma_commit(&bars->s_full[s]);
