@@ -94,7 +94,10 @@ int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, float* final_out,
   if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_colsoftmax_supported(c, p->dtype);
   if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc && c.s_scratch == nullptr) return FAWS_EBACKEND;
   cudaError_t e;
-  if (use_tc) {
+  if (c.s_scratch != nullptr) {  // buffered variant: stream the stored scores back
+    c.out = final_out;
+    e = launch_scratch_colsum(c, group_sum, s);
+  } else if (use_tc) {
     c.out = final_out;
     e = launch_tc_colsoftmax(c, p->dtype, group_sum, s);
   } else {

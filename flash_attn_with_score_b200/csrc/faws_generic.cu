@@ -335,6 +335,60 @@ __global__ void __launch_bounds__(NT) generic_colsoftmax_kernel(ColSoftmaxParams
   if (tid < BN && n0 + tid < p.n_end) p.out[bh * p.n_end + n0 + tid] = colacc;
 }
 
+// Second pass of the buffered cross-token variant: the scaled scores of the cross region were
+// stored by the forward pass as (B,Hq,M-split,split) fp32; this kernel streams them back
+// (attention_cross_token_softmax_sum.py:581-627, without atomics).  HBM-bound: a CTA owns 128
+// key columns, 4 row groups x 128 threads read rows i = split + rg, +4, ... (coalesced 512 B
+// per warp and row, 4 independent loads in flight per thread), accumulate
+// exp(s - L_i) in registers and are added in the fixed order rg0+rg1+rg2+rg3.
+__global__ void __launch_bounds__(512) scratch_colsum_kernel(ColSoftmaxParams p, int heads_per_cta, int Hout) {
+  __shared__ float red[3][128];
+  const int col = threadIdx.x & 127, rg = threadIdx.x >> 7;
+  const int j = blockIdx.x * 128 + col;
+  const int ho = blockIdx.y, b = blockIdx.z;
+  const int i_lo = max(max(p.i_begin, p.m_begin), p.split);
+  const bool col_ok = j < p.n_end && j < p.split;
+  const int rows = p.M - p.split;
+  float acc = 0.f;
+  for (int g = 0; g < heads_per_cta; ++g) {
+    const int h = ho * heads_per_cta + g;
+    const int64_t bh = (int64_t)b * p.Hq + h;
+    const float* sbase = p.s_scratch + bh * (int64_t)rows * p.split + j;
+    const float* Lbase = p.L + bh * p.M;
+    // key j is visible to query i iff j <= i + p_seq
+    int i0 = i_lo;
+    if (p.causal) i0 = max(i0, j - p.p_seq);
+    // rows of this row group: i = i_start, i_start + 4, ...
+    int i = i0 + ((rg - i0) & 3);
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (col_ok) {
+      for (; i + 12 < p.m_end; i += 16) {
+        const float s0 = __ldg(sbase + (int64_t)(i - p.split) * p.split);
+        const float s1 = __ldg(sbase + (int64_t)(i + 4 - p.split) * p.split);
+        const float s2 = __ldg(sbase + (int64_t)(i + 8 - p.split) * p.split);
+        const float s3 = __ldg(sbase + (int64_t)(i + 12 - p.split) * p.split);
+        const float L0 = Lbase[i], L1 = Lbase[i + 4], L2 = Lbase[i + 8], L3 = Lbase[i + 12];
+        a0 += (L0 == FAWS_NEG_INF) ? 0.f : exp2f((s0 - L0) * kLog2e);
+        a1 += (L1 == FAWS_NEG_INF) ? 0.f : exp2f((s1 - L1) * kLog2e);
+        a2 += (L2 == FAWS_NEG_INF) ? 0.f : exp2f((s2 - L2) * kLog2e);
+        a3 += (L3 == FAWS_NEG_INF) ? 0.f : exp2f((s3 - L3) * kLog2e);
+      }
+      for (; i < p.m_end; i += 4) {
+        const float s0 = __ldg(sbase + (int64_t)(i - p.split) * p.split);
+        const float L0 = Lbase[i];
+        a0 += (L0 == FAWS_NEG_INF) ? 0.f : exp2f((s0 - L0) * kLog2e);
+      }
+    }
+    acc += (a0 + a1) + (a2 + a3);
+  }
+  if (rg > 0) red[rg - 1][col] = acc;
+  __syncthreads();
+  if (rg == 0 && col_ok) {
+    const float total = ((acc + red[0][col]) + red[1][col]) + red[2][col];
+    p.out[((int64_t)b * Hout + ho) * p.n_end + j] = total;
+  }
+}
+
 // out[b,ho,j] = sum over the group's heads (or the single head) and over the
 // query blocks that visited column j, in a fixed order.
 __global__ void reduce_partials_kernel(ReducePartialParams p) {
@@ -423,6 +477,17 @@ cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cuda
     if ((e = set_smem(generic_colsoftmax_kernel<__nv_bfloat16>, smem)) != cudaSuccess) return e;
     generic_colsoftmax_kernel<__nv_bfloat16><<<grid, NT, smem, s>>>(p, vec);
   }
+  count_launch();
+  return cudaGetLastError();
+}
+
+// group_sum != 0: p.out is (B,Hk,n_end) and a CTA adds the G heads of its kv head; else (B,Hq,n_end).
+cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cudaStream_t s) {
+  if (p.n_end <= 0) return cudaSuccess;
+  const int hpc = group_sum ? p.G : 1;
+  const int Hout = p.Hq / hpc;
+  dim3 grid((p.n_end + 127) / 128, Hout, p.B);
+  scratch_colsum_kernel<<<grid, 512, 0, s>>>(p, hpc, Hout);
   count_launch();
   return cudaGetLastError();
 }

@@ -74,6 +74,7 @@ struct ReducePartialParams {
 // Launchers (each returns a cudaError_t from the launch).
 cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cudaStream_t s);
 cudaError_t launch_reduce_partials(const ReducePartialParams& p, cudaStream_t s);
 cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, int len,
                              cudaStream_t s);

@@ -216,14 +216,21 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if (!mbar_wait(&bars->kv_empty[s], (u & 1) ^ 1, abort_flag)) break;
         issue_kv_load(idx);
       }
-    } else if (warp == 1 && lane == 0 && nt > 0) {
+    } else if (warp == 1 && nt > 0) {
       // ---------------------------------------------------------- MMA issuer
+      // The whole warp runs this loop (converged control flow); inside each group one elected
+      // lane issues the tcgen05 instructions.
       constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
       constexpr uint32_t idesc_qk = make_idesc_f16(128, BN, kFmt, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, D, kFmt, 0, 1);
       // Operand descriptors are built once; inside the loops only compile-time offsets (in
       // 16-byte units) are added to their address field, so the issuing thread spends a few
       // instructions per MMA.
+#ifdef FAWS_TRACE
+      long long cyc_qk = 0, cyc_pv = 0, cyc_wait_p = 0, cyc_wait_kv = 0;
+      int n_qk = 0, n_pv = 0;
+      const long long c_role0 = clock64();
+#endif
       const uint64_t q_desc0 = make_desc_sw128(smem_u32(smem + L::q_off), 16, 1024);
       const uint64_t k_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), 16, 1024);
       const uint64_t v_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), L::kSub, 1024);
@@ -237,28 +244,54 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const uint64_t qd = q_desc0 + (uint64_t)(t * (L::kTile >> 4));
         const uint64_t kd = k_desc0 + (uint64_t)(slot * (L::kTile >> 4));
         const uint32_t d_tmem = tmem_base + (uint32_t)(t * BN);
+        if (elect_one()) {
+#ifdef FAWS_TRACE
+          const long long c0 = clock64();
+#endif
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
-          if (kk == 0) mma_ss(d_tmem, qd + off, kd + off, idesc_qk, 0u);
-          else mma_ss_acc(d_tmem, qd + off, kd + off, idesc_qk);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
+            if (kk == 0) mma_ss(d_tmem, qd + off, kd + off, idesc_qk, 0u);
+            else mma_ss_acc(d_tmem, qd + off, kd + off, idesc_qk);
+          }
+          mma_commit(&bars->s_full[t]);
+#ifdef FAWS_TRACE
+          cyc_qk += clock64() - c0; ++n_qk;
+#endif
         }
-        mma_commit(&bars->s_full[t]);
+        __syncwarp();
       };
       // O_t (+)= P_t . V; P_t sits in the first 64 columns of S_t (two 16-bit values per column)
       auto issue_pv = [&](int t, int slot, bool accumulate) {
         const uint64_t vd = v_desc0 + (uint64_t)(slot * (L::kTile >> 4));
         const uint32_t d_tmem = tmem_base + 256 + (uint32_t)(t * BN);
         const uint32_t a_tmem = tmem_base + (uint32_t)(t * BN);
+        if (elect_one()) {
+#ifdef FAWS_TRACE
+          const long long c0 = clock64();
+#endif
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t off = (uint64_t)((kk * 16 * 128) >> 4);
-          if (kk == 0) mma_ts(d_tmem, a_tmem, vd, idesc_pv, accumulate ? 1u : 0u);
-          else mma_ts_acc(d_tmem, a_tmem + (uint32_t)(kk * 8), vd + off, idesc_pv);
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            const uint64_t off = (uint64_t)((kk * 16 * 128) >> 4);
+            if (kk == 0) mma_ts(d_tmem, a_tmem, vd, idesc_pv, accumulate ? 1u : 0u);
+            else mma_ts_acc(d_tmem, a_tmem + (uint32_t)(kk * 8), vd + off, idesc_pv);
+          }
+#ifdef FAWS_TRACE
+          cyc_pv += clock64() - c0; ++n_pv;
+#endif
         }
+        __syncwarp();
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (elect_one()) mma_commit(bar);
+        __syncwarp();
       };
       int cnt[2] = {0, 0};  // key tiles each query tile has been given so far
-      TRACE_DECL(2)
+#ifdef FAWS_TRACE
+      const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0);
+      int tr_n = 0;
+      long long* tr_buf = g_trace + 2 * 4096;
+#endif
       TRACE(0);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
       if (ok) ok = kv_wait(0);
@@ -266,7 +299,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const int t0 = tile_of(0);
         if (t0 < nt_q[0]) issue_qk(0, 0);
         if (t0 < nt_q[1]) issue_qk(1, 0);
-        mma_commit(&bars->kv_empty[0]);
+        commit(&bars->kv_empty[0]);
       }
       for (int it = 0; ok && it < nt; ++it) {
         const int tk = tile_of(it);
@@ -295,13 +328,27 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           issue_pv(1, v_slot, cnt[1] > 0);
           ++cnt[1];
         }
-        mma_commit(&bars->kv_empty[v_slot]);
+        commit(&bars->kv_empty[v_slot]);
         if (more) {
           if (tk_next < nt_q[1]) issue_qk(1, k_slot);
-          mma_commit(&bars->kv_empty[k_slot]);
+          commit(&bars->kv_empty[k_slot]);
         }
       }
-      if (ok) mma_commit(&bars->o_done);
+      if (ok) commit(&bars->o_done);
+#ifdef FAWS_TRACE
+      // the elected lane differs from lane 0 in general: reduce the counters over the warp
+      for (int o = 16; o > 0; o >>= 1) {
+        cyc_qk += __shfl_xor_sync(0xffffffffu, cyc_qk, o);
+        cyc_pv += __shfl_xor_sync(0xffffffffu, cyc_pv, o);
+        n_qk += __shfl_xor_sync(0xffffffffu, n_qk, o);
+        n_pv += __shfl_xor_sync(0xffffffffu, n_pv, o);
+      }
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
+        g_trace[2 * 4096 + 4000] = cyc_qk; g_trace[2 * 4096 + 4001] = n_qk;
+        g_trace[2 * 4096 + 4002] = cyc_pv; g_trace[2 * 4096 + 4003] = n_pv;
+        g_trace[2 * 4096 + 4004] = clock64() - c_role0;
+      }
+#endif
       TRACE_END();
     }
   } else {
@@ -497,15 +544,23 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       return true;
     };
 
+#ifdef FAWS_TRACE
+    long long cyc_wait_s = 0; int n_tiles = 0;
+    const long long c_loop0 = clock64();
+#endif
     {
       int cnt = 0;
       for (int it = 0; it < nt; ++it) {
         const int tk = tile_of(it);
         if (tk >= my_nt) continue;
         const int n0 = tk * BN;
-        TRACE(19);
+#ifdef FAWS_TRACE
+        const long long cw0 = clock64();
+#endif
         if (!mbar_wait(&bars->s_full[qt], cnt & 1, abort_flag)) { alive = false; break; }
-        TRACE(20);
+#ifdef FAWS_TRACE
+        cyc_wait_s += clock64() - cw0; ++n_tiles;
+#endif
         tc_fence_after();
         const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= r_tile + p.p_seq));
         const bool ok = full_vis ? tile_body(std::false_type{}, cnt, n0) : tile_body(std::true_type{}, cnt, n0);
@@ -514,6 +569,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
     }
     const float rs = rs_raw * scale;
+#ifdef FAWS_TRACE
+    if (tr_on) {
+      g_trace[2 * 4096 + 4010 + qt * 4] = cyc_wait_s; g_trace[2 * 4096 + 4011 + qt * 4] = n_tiles;
+      g_trace[2 * 4096 + 4012 + qt * 4] = clock64() - c_loop0;
+    }
+#endif
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
     if (alive && my_nt > 0) {
@@ -703,8 +764,9 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           tma_load_4d(smem + L::q_off + s * L::kTile + c * L::kSub, &maps.q, &bars->q_full[s], c * 64, qt * BM,
                       h0 + g, b);
       }
-    } else if (warp == 1 && lane == 0 && total > 0) {
+    } else if (warp == 1 && total > 0) {
       // ---------------------------------------------------------- MMA issuer: S^T = K . Q^T
+      // (whole warp in the loop, one elected lane issues)
       constexpr int kFmt = std::is_same<T, __half>::value ? 0 : 1;
       constexpr uint32_t idesc = make_idesc_f16(128, BM, kFmt, 0, 0);
       const uint64_t k_desc = make_desc_sw128(smem_u32(smem + L::k_off), 16, 1024);
@@ -717,14 +779,17 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
         tc_fence_after();
         const uint64_t qd = q_desc0 + (uint64_t)(s * (L::kTile >> 4));
         const uint32_t d_tmem = tmem_base + (uint32_t)(s * BM);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
-          if (kk == 0) mma_ss(d_tmem, k_desc + off, qd + off, idesc, 0u);
-          else mma_ss_acc(d_tmem, k_desc + off, qd + off, idesc);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
+            if (kk == 0) mma_ss(d_tmem, k_desc + off, qd + off, idesc, 0u);
+            else mma_ss_acc(d_tmem, k_desc + off, qd + off, idesc);
+          }
+          mma_commit(&bars->q_empty[s]);
+          mma_commit(&bars->s_full[s]);
         }
-        mma_commit(&bars->q_empty[s]);
-        mma_commit(&bars->s_full[s]);
+        __syncwarp();
       }
     }
   } else {

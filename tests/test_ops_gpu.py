@@ -233,3 +233,50 @@ def test_tcgen05_family_is_used_and_matches(shape, causal, dtype):
     _check_sum(xb, xs_ref, "cross_softmax_buffered")
     o, sc = F.attention_with_softmax_col_sum(qd, kd, vd, causal)
     _check_sum(sc, orc.group_sum(orc.softmax_col_sum(ref_scores), Hk), "softmax_col_sum")
+
+
+def _query_split_worker(rank, world, port, q, k, v, split, want_col, want_x):
+    import os
+
+    import torch.distributed as dist
+
+    from flash_attn_with_score_b200 import shard
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        qd, kd, vd = q.cuda(rank), k.cuda(rank), v.cuda(rank)
+        out, col, (b, e) = shard.query_split(F.attention_with_softmax_col_sum, qd, kd, vd, False)
+        ok, viol = orc.check_sum(col.cpu(), want_col)
+        assert ok, f"rank {rank}: query-split softmax col sum {viol}"
+        out2, x, _ = shard.query_split(F.attention_cross_token_qk_sum, qd, kd, vd, split, True)
+        ok, viol = orc.check_sum(x.cpu(), want_x)
+        assert ok, f"rank {rank}: query-split cross-token qk sum {viol}"
+        # every rank holds the same bits
+        gathered = [torch.empty_like(col) for _ in range(world)]
+        dist.all_gather(gathered, col)
+        assert all(torch.equal(g, gathered[0]) for g in gathered)
+        assert F.device_status() == 0
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_query_split_two_gpus_nccl():
+    """Query rows of every head split over 2 ranks; column-type sums all-gathered and reduced in rank order."""
+    import socket
+
+    import torch.multiprocessing as mp
+    shape = (1, 4, 2, 512, 512, 128)
+    q, k, v = _inputs(shape, torch.float16, seed=31)
+    _, sc_full = _oracle(q, k, v, False)
+    _, sc_causal = _oracle(q, k, v, True)
+    want_col = orc.group_sum(orc.softmax_col_sum(sc_full), 2)
+    want_x = orc.group_sum(orc.cross_token_qk_sum(sc_causal, 256), 2)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_query_split_worker, args=(2, port, q, k, v, 256, want_col, want_x), nprocs=2, join=True)
