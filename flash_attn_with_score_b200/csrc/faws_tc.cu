@@ -47,8 +47,11 @@ constexpr int TMEM_COLS = 512;
 // CTA per SM); after re-allocation the total must not exceed that pool, otherwise the
 // .inc never returns.
 constexpr int REGS_LAUNCH = 168;
-constexpr int REGS_AUX = 40;
-constexpr int REGS_SOFTMAX = 232;
+#ifndef FAWS_REGS_AUX
+#define FAWS_REGS_AUX 56
+#endif
+constexpr int REGS_AUX = FAWS_REGS_AUX;
+constexpr int REGS_SOFTMAX = ((REGS_LAUNCH * NTHREADS - 128 * REGS_AUX) / 256) & ~7;
 static_assert(128 * REGS_AUX + 256 * REGS_SOFTMAX <= REGS_LAUNCH * NTHREADS, "setmaxnreg would block");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -373,7 +376,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     const int qb128 = r_tile / BM;
     const bool part_on = HOOK == kHookColPart && qb128 >= p.qb_first && r_tile < p.m_end;
     const float masked_f = __uint_as_float(p.masked_bits);
-    int n_stage = 0;  // staging-buffer uses so far (this warp)
 
     float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
     bool alive = true;
@@ -484,37 +486,46 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         rs_raw += (s0 + s1) + (s2 + s3);
       }
       if constexpr (store_scores || store_scratch) {
+        // Two rounds of two 32-column chunks: both 4 KB staging buffers are rewritten per round,
+        // one proxy fence per round, lanes 0 and 1 each issue (and later wait for) one TMA store.
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int jb = n0 + c * 32;
-          const bool do_scratch = store_scratch && (r_tile + lg * 32 >= p.split) && (jb < p.split);
-          if (store_scores || do_scratch) {
-            unsigned char* sb = stage + (n_stage & 1) * 4096;
-            if (lane == 0) tma_store_wait_read<1>();
+        for (int half = 0; half < 2; ++half) {
+          const bool rows_in = store_scores || (r_tile + lg * 32 >= p.split);
+          const bool round_on = rows_in && (store_scores || n0 + half * 64 < p.split);
+          if (round_on) {
+            if (lane < 2) tma_store_wait_read<0>();
             __syncwarp();
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
-              float4 val;
-              val.x = __uint_as_float(r[c * 32 + cc * 4 + 0]) * scale;
-              val.y = __uint_as_float(r[c * 32 + cc * 4 + 1]) * scale;
-              val.z = __uint_as_float(r[c * 32 + cc * 4 + 2]) * scale;
-              val.w = __uint_as_float(r[c * 32 + cc * 4 + 3]) * scale;
-              if (kMasked && store_scores) {
-                if (!(c * 32 + cc * 4 + 0 < nvis)) val.x = masked_f;
-                if (!(c * 32 + cc * 4 + 1 < nvis)) val.y = masked_f;
-                if (!(c * 32 + cc * 4 + 2 < nvis)) val.z = masked_f;
-                if (!(c * 32 + cc * 4 + 3 < nvis)) val.w = masked_f;
+            for (int c2 = 0; c2 < 2; ++c2) {
+              const int c = half * 2 + c2;
+              unsigned char* sb = stage + c2 * 4096;
+#pragma unroll
+              for (int cc = 0; cc < 8; ++cc) {
+                float4 val;
+                val.x = __uint_as_float(r[c * 32 + cc * 4 + 0]) * scale;
+                val.y = __uint_as_float(r[c * 32 + cc * 4 + 1]) * scale;
+                val.z = __uint_as_float(r[c * 32 + cc * 4 + 2]) * scale;
+                val.w = __uint_as_float(r[c * 32 + cc * 4 + 3]) * scale;
+                if (kMasked && store_scores) {
+                  if (!(c * 32 + cc * 4 + 0 < nvis)) val.x = masked_f;
+                  if (!(c * 32 + cc * 4 + 1 < nvis)) val.y = masked_f;
+                  if (!(c * 32 + cc * 4 + 2 < nvis)) val.z = masked_f;
+                  if (!(c * 32 + cc * 4 + 3 < nvis)) val.w = masked_f;
+                }
+                *reinterpret_cast<float4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = val;
               }
-              *reinterpret_cast<float4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = val;
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-              if (store_scores) tma_store_3d(&maps.st, sb, jb, r_tile + lg * 32 - p.m_begin, bh);
-              else tma_store_3d(&maps.st, sb, jb, r_tile + lg * 32 - p.split, bh);
+            if (lane < 2) {
+              const int jb = n0 + (half * 2 + lane) * 32;
+              if (store_scores) {
+                tma_store_3d(&maps.st, stage + lane * 4096, jb, r_tile + lg * 32 - p.m_begin, bh);
+              } else if (jb < p.split) {
+                tma_store_3d(&maps.st, stage + lane * 4096, jb, r_tile + lg * 32 - p.split, bh);
+              }
               tma_store_commit();
             }
-            ++n_stage;
           }
         }
       }
@@ -544,23 +555,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       return true;
     };
 
-#ifdef FAWS_TRACE
-    long long cyc_wait_s = 0; int n_tiles = 0;
-    const long long c_loop0 = clock64();
-#endif
     {
       int cnt = 0;
       for (int it = 0; it < nt; ++it) {
         const int tk = tile_of(it);
         if (tk >= my_nt) continue;
         const int n0 = tk * BN;
-#ifdef FAWS_TRACE
-        const long long cw0 = clock64();
-#endif
+        TRACE(19);
         if (!mbar_wait(&bars->s_full[qt], cnt & 1, abort_flag)) { alive = false; break; }
-#ifdef FAWS_TRACE
-        cyc_wait_s += clock64() - cw0; ++n_tiles;
-#endif
+        TRACE(20);
         tc_fence_after();
         const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= r_tile + p.p_seq));
         const bool ok = full_vis ? tile_body(std::false_type{}, cnt, n0) : tile_body(std::true_type{}, cnt, n0);
@@ -569,12 +572,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
     }
     const float rs = rs_raw * scale;
-#ifdef FAWS_TRACE
-    if (tr_on) {
-      g_trace[2 * 4096 + 4010 + qt * 4] = cyc_wait_s; g_trace[2 * 4096 + 4011 + qt * 4] = n_tiles;
-      g_trace[2 * 4096 + 4012 + qt * 4] = clock64() - c_loop0;
-    }
-#endif
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
     if (alive && my_nt > 0) {
@@ -624,7 +621,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs;
       }
       if constexpr (store_scores) if (my_nt * BN < p.N) {
-        if (lane == 0) tma_store_wait_read<0>();
+        if (lane < 2) tma_store_wait_read<0>();
         __syncwarp();
         const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
 #pragma unroll
@@ -639,7 +636,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
     }
     TRACE(31);
-    if (lane == 0) tma_store_wait<0>();
+    if (lane < 2) tma_store_wait<0>();
     TRACE(32);
     TRACE_END();
   }
