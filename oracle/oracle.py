@@ -148,7 +148,7 @@ def linear_col_sum(q, k, causal, sm_scale=None, p_seq=0, i_begin=0, n_end=None):
         # suffix[i] = sum_{i' >= i} q_i'; key j sees queries i >= max(j - p_seq, 0)
         suffix = torch.flip(torch.cumsum(torch.flip(qz, dims=[2]), dim=2), dims=[2])
         suffix = torch.cat([suffix, torch.zeros_like(suffix[:, :, :1])], dim=2)
-        first = (torch.arange(n_end) - p_seq).clamp(min=0, max=M)
+        first = (torch.arange(n_end, device=q.device) - p_seq).clamp(min=0, max=M)
         qs = suffix[:, :, first]
     else:
         qs = qz.sum(dim=2, keepdim=True).expand(B, Hq, n_end, D)
@@ -167,7 +167,7 @@ def linear_row_sum(q, k, causal, sm_scale=None, p_seq=0):
     if causal:
         prefix = torch.cumsum(k, dim=2)
         prefix = torch.cat([torch.zeros_like(prefix[:, :, :1]), prefix], dim=2)
-        cnt = (torch.arange(M) + p_seq + 1).clamp(min=0, max=N)
+        cnt = (torch.arange(M, device=q.device) + p_seq + 1).clamp(min=0, max=N)
         ks = prefix[:, :, cnt]
     else:
         ks = k.sum(dim=2, keepdim=True).expand(B, Hq, M, D)
