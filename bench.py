@@ -135,6 +135,14 @@ class ClockSampler:
 
 def make_inputs(cfg, seed, device, S=None):
     S = cfg["S"] if S is None else S
+    if device is not None and cfg["B"] * cfg["Hq"] * S * cfg["D"] > (1 << 27):
+        # very large configs (cfg5): draw on the device, the CPU generator would take many seconds
+        g = torch.Generator(device=device).manual_seed(seed)
+        mk = lambda h: torch.randn(cfg["B"], h, S, cfg["D"], device=device, generator=g)  # noqa: E731
+        q, k, v = mk(cfg["Hq"]), mk(cfg["Hk"]), mk(cfg["Hk"])
+        if cfg.get("vdist") == "uniform":
+            v = torch.rand(cfg["B"], cfg["Hk"], S, cfg["D"], device=device, generator=g) * 2 - 1
+        return q.to(cfg["dtype"]), k.to(cfg["dtype"]), v.to(cfg["dtype"])
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(cfg["B"], cfg["Hq"], S, cfg["D"], generator=g).to(cfg["dtype"])
     k = torch.randn(cfg["B"], cfg["Hk"], S, cfg["D"], generator=g).to(cfg["dtype"])
@@ -209,6 +217,7 @@ def ops_table(F, device, pk):
     rows = []
     cfg3 = dict(B=1, Hq=28, Hk=4, S=4096, D=128, dtype=torch.bfloat16, causal=True, vscale=0.5)
     cfg4 = dict(B=2, Hq=32, Hk=8, S=4096, D=128, dtype=torch.float16, causal=True)
+    cfg5 = dict(B=4, Hq=32, Hk=8, S=16384, D=128, dtype=torch.bfloat16, causal=False, vdist="uniform")
     plans = [
         ("cfg3", cfg3, None, [("attention", F.attention), ("row_sum", F.attention_with_row_sum),
                               ("col_sum", F.attention_with_col_sum),
@@ -217,6 +226,8 @@ def ops_table(F, device, pk):
         ("cfg4", cfg4, 3072, [("cross_qk", F.attention_cross_token_qk_sum),
                               ("cross_softmax", F.attention_cross_token_softmax_sum),
                               ("cross_softmax_buffered", F.attention_cross_token_softmax_sum_buffered)]),
+        ("cfg5", cfg5, None, [("softmax_col_sum", F.attention_with_softmax_col_sum)]),
+        ("cfg5", cfg5, 12288, [("cross_softmax", F.attention_cross_token_softmax_sum)]),
     ]
     for name, cfg, split, ops in plans:
         q, k, v = make_inputs(cfg, 0, device)
@@ -225,7 +236,7 @@ def ops_table(F, device, pk):
                 call = lambda: fn(q, k, v, cfg["causal"])  # noqa: E731
             else:
                 call = lambda: fn(q, k, v, split, cfg["causal"])  # noqa: E731
-            ms = time_op(call, 5, 3)
+            ms = time_op(call, 5, 3 if name != "cfg5" else 1)
             flops, nbytes = algorithmic(cfg, "scores" if op == "attention" else op, split)
             if op == "attention":
                 nbytes -= cfg["B"] * cfg["Hq"] * cfg["S"] * cfg["S"] * 4

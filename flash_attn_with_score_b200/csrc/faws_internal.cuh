@@ -43,6 +43,7 @@ struct FwdParams {
   int n_qb_part;         // partial rows per (b,h)
   float* s_scratch;      // buffered variant: (B,Hq,M-split,split) scaled scores
   int split;
+  int lpt_order;         // set by the tcgen05 launcher: heaviest causal row blocks of all heads first
 };
 
 // Key-major softmax column-sum pass: out[b,h,j] = sum_{i>=i_begin, visible} exp(s_ij - L_i).

@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -39,9 +40,8 @@ using namespace ptx;
 
 constexpr int BM = kTcBlockM;   // rows of one query tile
 constexpr int BN = kTcBlockN;
-constexpr int CTA_ROWS = 2 * BM;
 constexpr int NTHREADS = 384;
-constexpr int KV_SLOTS = 3;
+constexpr int MAX_KV_SLOTS = 4;
 constexpr int TMEM_COLS = 512;
 // setmaxnreg budget: the CTA is launched with 168 registers per thread (384 threads, one
 // CTA per SM); after re-allocation the total must not exceed that pool, otherwise the
@@ -59,6 +59,8 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #define FAWS_NEG_INF (__int_as_float(0xff800000))
 
 #ifdef FAWS_TRACE
+__device__ long long g_cta_times[4096 * 3];
+__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 __device__ long long g_trace[3 * 4096];
 #define TRACE_DECL(role) const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0); int tr_n = 0; long long* tr_buf = g_trace + (role) * 4096;
 #define TRACE(tag) do { if (tr_on && tr_n < 2040) { tr_buf[2 * tr_n] = (tag); tr_buf[2 * tr_n + 1] = clock64(); ++tr_n; } } while (0)
@@ -74,13 +76,20 @@ struct TcMaps {
   CUtensorMap st;          // scores (or score-scratch) store map
 };
 
-template <int D>
+// SPLIT = false: the CTA owns two query tiles (256 rows), one per softmax warpgroup.
+// SPLIT = true : the CTA owns one query tile (128 rows) and the two warpgroups take alternate
+//                key tiles of it (their partial O, m, l are merged at the end), which halves
+//                the longest dependent chain; used when a launch has few CTAs.
+template <int D, bool SPLIT>
 struct Smem {
   static constexpr int kTile = 128 * D * 2;  // one Q / K / V tile
   static constexpr int kSub = 128 * 128;     // one 64-element-wide sub-tile: 128 rows x 128 B
-  static constexpr int q_off = 0;                          // 2 query tiles
-  static constexpr int kv_off = q_off + 2 * kTile;         // K/V ring
-  static constexpr int stage_off = kv_off + KV_SLOTS * kTile;  // 8 warps x 2 x 4 KB
+  static constexpr int kQTiles = SPLIT ? 1 : 2;
+  static constexpr int kSlots = SPLIT ? 4 : 3;
+  static constexpr int kRows = kQTiles * 128;
+  static constexpr int q_off = 0;                             // query tile(s)
+  static constexpr int kv_off = q_off + kQTiles * kTile;      // K/V ring
+  static constexpr int stage_off = kv_off + kSlots * kTile;   // 8 warps x 2 x 4 KB
   static constexpr int bar_off = stage_off + 8 * 2 * 4096;
   static constexpr int total = bar_off + 256;
   static constexpr int alloc = total + 1024;  // slack to align the base to 1024 B
@@ -88,11 +97,12 @@ struct Smem {
 
 struct Bars {
   uint64_t q_full;
-  uint64_t kv_full[KV_SLOTS], kv_empty[KV_SLOTS];
+  uint64_t kv_full[MAX_KV_SLOTS], kv_empty[MAX_KV_SLOTS];
   uint64_t s_full[2];     // per query tile: S_t written by the tensor pipe
   uint64_t p_ready[2];    // per query tile: P_t written by its 128 softmax threads
   uint64_t col_ready[2];  // per query tile: column-sum partial rows of its 4 warps are in smem
   uint64_t o_done;        // every MMA of the CTA has completed
+  uint64_t merge_ready;   // SPLIT: warpgroup 1 has published its (m, l, row sum)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -125,12 +135,20 @@ __device__ __forceinline__ void warp_column_sums(float (&v)[32], int lane) {
 // Score-tile hook compiled into a kernel instance (one per operator family).
 enum Hook : int { kHookNone = 0, kHookScores = 1, kHookRowSum = 2, kHookColPart = 3, kHookScratch = 4 };
 
-template <typename T, int D, int HOOK>
+template <typename T, int D, int HOOK, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __restrict__ status) {
-  using L = Smem<D>;
+  using L = Smem<D, SPLIT>;
+  constexpr int KV_SLOTS = L::kSlots;
+  constexpr int CTA_ROWS = L::kRows;
 #ifdef FAWS_TRACE
   const long long t_entry = clock64();
+  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (threadIdx.x == 0 && cta_lin < 4096) {
+    g_cta_times[cta_lin * 3] = gtimer();
+    unsigned smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    g_cta_times[cta_lin * 3 + 2] = smid;
+  }
 #endif
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -139,18 +157,24 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ncb = gridDim.x;
-  const int cb_rel = ncb - 1 - (int)blockIdx.x;  // heaviest (last) causal blocks first
+  // Launch order.  Default: row blocks fastest, so the CTAs of a head run together and share its
+  // K/V through L2.  lpt_order (causal, K/V small enough to stay in L2 anyway): row blocks
+  // slowest, so the heaviest row blocks of every head are dispatched first (longest-processing-
+  // time-first packing of the causal triangle onto the SMs).
+  const int ncb = p.lpt_order ? gridDim.z : gridDim.x;
+  const int cb_rel = ncb - 1 - (int)(p.lpt_order ? blockIdx.z : blockIdx.x);  // heaviest (last) blocks first
   const int m0 = p.m_begin + cb_rel * CTA_ROWS;
   const int cb_abs = m0 / CTA_ROWS;
-  const int h = blockIdx.y, b = blockIdx.z, hk = h / p.G;
+  const int h = p.lpt_order ? blockIdx.x : blockIdx.y;
+  const int b = p.lpt_order ? blockIdx.y : blockIdx.z;
+  const int hk = h / p.G;
   const int bh = b * p.Hq + h;
 
   // key tiles each query tile visits (0 for a tile that lies outside the row window)
   int nt_q[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int r0 = m0 + t * BM;
+    const int r0 = m0 + (SPLIT ? 0 : t * BM);
     int hi = 0;
     if (r0 < p.m_end) {
       hi = p.N;
@@ -188,13 +212,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       mbar_init(&bars->col_ready[t], 128);
     }
     mbar_init(&bars->o_done, 1);
+    mbar_init(&bars->merge_ready, 128);
     bars->abort_flag = 0;
     mbar_fence_init();
     // This thread is also the TMA producer: start the first loads now so that their HBM
     // latency overlaps the TMEM allocation and the set-up barrier.
     if (nt > 0) {
-      mbar_arrive_expect_tx(&bars->q_full, 2 * L::kTile);
-      for (int t = 0; t < 2; ++t)
+      mbar_arrive_expect_tx(&bars->q_full, L::kQTiles * L::kTile);
+      for (int t = 0; t < L::kQTiles; ++t)
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
                       m0 - p.m_begin + t * BM, h, b);
@@ -244,7 +269,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       };
       // S_t = Q_t . K^T for the key tile in ring slot `slot`
       auto issue_qk = [&](int t, int slot) {
-        const uint64_t qd = q_desc0 + (uint64_t)(t * (L::kTile >> 4));
+        const uint64_t qd = q_desc0 + (uint64_t)((SPLIT ? 0 : t) * (L::kTile >> 4));
         const uint64_t kd = k_desc0 + (uint64_t)(slot * (L::kTile >> 4));
         const uint32_t d_tmem = tmem_base + (uint32_t)(t * BN);
         if (elect_one()) {
@@ -289,7 +314,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if (elect_one()) mma_commit(bar);
         __syncwarp();
       };
-      int cnt[2] = {0, 0};  // key tiles each query tile has been given so far
+      int cnt[2] = {0, 0};  // key tiles each warpgroup has been given so far
 #ifdef FAWS_TRACE
       const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0);
       int tr_n = 0;
@@ -297,6 +322,28 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 #endif
       TRACE(0);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      if constexpr (SPLIT) {
+        // Visiting index `it` belongs to warpgroup it & 1.  Before S of that warpgroup is
+        // overwritten by Q.K^T of tile it, the P.V of its previous tile (it - 2) is issued.
+        for (int it = 0; ok && it < nt + 2; ++it) {
+          const int w = it & 1;
+          if (it >= 2) {
+            const int v_idx = 2 * (it - 2) + 1;
+            if (!(ok = kv_wait(v_idx))) break;
+            if (!(ok = mbar_wait(&bars->p_ready[w], cnt[w] & 1, abort_flag))) break;
+            tc_fence_after();
+            issue_pv(w, v_idx % KV_SLOTS, cnt[w] > 0);
+            ++cnt[w];
+            commit(&bars->kv_empty[v_idx % KV_SLOTS]);
+          }
+          if (it < nt) {
+            if (!(ok = kv_wait(2 * it))) break;
+            issue_qk(w, (2 * it) % KV_SLOTS);
+            commit(&bars->kv_empty[(2 * it) % KV_SLOTS]);
+          }
+        }
+        ok = ok && true;
+      } else {
       if (ok) ok = kv_wait(0);
       if (ok) {
         const int t0 = tile_of(0);
@@ -337,6 +384,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           commit(&bars->kv_empty[k_slot]);
         }
       }
+      }  // !SPLIT
       if (ok) commit(&bars->o_done);
 #ifdef FAWS_TRACE
       // the elected lane differs from lane 0 in general: reduce the counters over the warp
@@ -357,10 +405,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   } else {
     reg_alloc<REGS_SOFTMAX>();
     // ------------------------------------------------------------ softmax warps
-    const int qt = (warp - 4) >> 2;  // query tile of this warpgroup
+    const int qt = (warp - 4) >> 2;  // warpgroup: its query tile (or, SPLIT, its half of the key tiles)
     const int lg = warp & 3;         // TMEM lane group this warp may touch
     const int row = lg * 32 + lane;
-    const int r_tile = m0 + qt * BM;  // first row of the query tile
+    const int r_tile = m0 + (SPLIT ? 0 : qt * BM);  // first row of the query tile
     const int i = r_tile + row;
     const int my_nt = nt_q[qt];
     const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
@@ -559,7 +607,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       int cnt = 0;
       for (int it = 0; it < nt; ++it) {
         const int tk = tile_of(it);
-        if (tk >= my_nt) continue;
+        if (SPLIT ? ((it & 1) != qt) : (tk >= my_nt)) continue;
         const int n0 = tk * BN;
         TRACE(19);
         if (!mbar_wait(&bars->s_full[qt], cnt & 1, abort_flag)) { alive = false; break; }
@@ -579,24 +627,65 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       tc_fence_after();
     }
     TRACE(30);
-    if (alive && r_tile < p.m_end) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    // SPLIT: warpgroup 1 publishes its running state; warpgroup 0 merges the two partial results.
+    float* merge = reinterpret_cast<float*>(smem + L::kv_off);  // ring is free after o_done
+    bool write_out = alive && r_tile < p.m_end;
+    float l_all = l_run, m_all = m_run, w0 = 1.f, w1 = 0.f;
+    float rs_all = rs;
+    bool have1 = false;
+    if constexpr (SPLIT) {
+      if (qt == 1) {
+        merge[row] = m_run;
+        merge[128 + row] = l_run;
+        merge[256 + row] = rs;
+        mbar_arrive(&bars->merge_ready);
+        write_out = false;
+      } else {
+        if (!mbar_wait(&bars->merge_ready, 0, abort_flag)) { alive = false; write_out = false; }
+        const float m1 = merge[row], l1 = merge[128 + row];
+        rs_all = rs + merge[256 + row];
+        have1 = nt > 1;  // warpgroup 1 processed at least one tile
+        m_all = fmaxf(m_run, m1);
+        w0 = (m_run == FAWS_NEG_INF) ? 0.f : fast_exp2(m_run - m_all);
+        w1 = (m1 == FAWS_NEG_INF) ? 0.f : fast_exp2(m1 - m_all);
+        l_all = l_run * w0 + l1 * w1;
+      }
+    }
+    if (write_out) {
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       if (my_nt > 0) {
         // Every MMA of the CTA has completed, so the Q tiles' shared memory is free: each warp
         // stages its 32 x D output block there (128B-swizzled) and stores it with TMA.
         unsigned char* ost = smem + L::q_off + (warp - 4) * (32 * D * 2);
+        const float f0 = w0 * inv, f1 = w1 * inv;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t ro[32];
           tmem_ld32(t_o + c * 32, ro);
           tmem_wait_ld();
+          if constexpr (SPLIT) {
+            if (have1) {
+              uint32_t r1[32];
+              tmem_ld32(t_o + BN + c * 32, r1);  // warpgroup 1's accumulator, same lanes
+              tmem_wait_ld();
+#pragma unroll
+              for (int x = 0; x < 32; ++x)
+                ro[x] = __float_as_uint(__uint_as_float(ro[x]) * f0 + __uint_as_float(r1[x]) * f1);
+            } else {
+#pragma unroll
+              for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * f0);
+            }
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * inv);
+          }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 w;
-            w.x = pack2<T>(__uint_as_float(ro[g * 8 + 0]) * inv, __uint_as_float(ro[g * 8 + 1]) * inv);
-            w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]) * inv, __uint_as_float(ro[g * 8 + 3]) * inv);
-            w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]) * inv, __uint_as_float(ro[g * 8 + 5]) * inv);
-            w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]) * inv, __uint_as_float(ro[g * 8 + 7]) * inv);
+            w.x = pack2<T>(__uint_as_float(ro[g * 8 + 0]), __uint_as_float(ro[g * 8 + 1]));
+            w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]), __uint_as_float(ro[g * 8 + 3]));
+            w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]), __uint_as_float(ro[g * 8 + 5]));
+            w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]), __uint_as_float(ro[g * 8 + 7]));
             const int cc = (c & 1) * 4 + g;  // 16-byte chunk inside the 64-column sub-tile
             *reinterpret_cast<uint4*>(ost + (c >> 1) * 4096 + lane * 128 + ((cc ^ (lane & 7)) << 4)) = w;
           }
@@ -617,22 +706,25 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
       if (row_ok) {
         if (p.L != nullptr)
-          p.L[(int64_t)bh * p.M + i] = l_run > 0.f ? (m_run + log2f(l_run)) * kLn2 : FAWS_NEG_INF;
-        if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs;
+          p.L[(int64_t)bh * p.M + i] = l_all > 0.f ? (m_all + log2f(l_all)) * kLn2 : FAWS_NEG_INF;
+        if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs_all;
       }
-      if constexpr (store_scores) if (my_nt * BN < p.N) {
-        if (lane < 2) tma_store_wait_read<0>();
-        __syncwarp();
-        const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
+    }
+    if constexpr (store_scores) if (alive && r_tile < p.m_end && my_nt * BN < p.N) {
+      if (lane < 2) tma_store_wait_read<0>();
+      __syncwarp();
+      const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<float4*>(stage + lane * 128 + (cc << 4)) = fill;
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int r0 = r_tile + lg * 32 - p.m_begin;
-          for (int j0 = my_nt * BN; j0 < p.N; j0 += 32) tma_store_3d(&maps.st, stage, j0, r0, bh);
-          tma_store_commit();
+      for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<float4*>(stage + lane * 128 + (cc << 4)) = fill;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int r0 = r_tile + lg * 32 - p.m_begin;
+        for (int j0 = my_nt * BN; j0 < p.N; j0 += 32) {
+          // SPLIT: the two warpgroups share the rows, so they take alternate key tiles
+          if (!SPLIT || ((j0 / BN) & 1) == qt) tma_store_3d(&maps.st, stage, j0, r0, bh);
         }
+        tma_store_commit();
       }
     }
     TRACE(31);
@@ -654,6 +746,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+#ifdef FAWS_TRACE
+  if (threadIdx.x == 0 && cta_lin < 4096) g_cta_times[cta_lin * 3 + 1] = gtimer();
+#endif
 }
 
 // ---------------------------------------------------------------------------- key-major pass
@@ -965,21 +1060,45 @@ int* device_status_word() {
   return words[dev];
 }
 
-template <typename T, int D, int HOOK>
-cudaError_t launch_fwd_h(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
-  using L = Smem<D>;
+template <typename T, int D, int HOOK, bool SPLIT>
+cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
+  using L = Smem<D, SPLIT>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e =
-        cudaFuncSetAttribute(tc_fwd_kernel<T, D, HOOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
+    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<T, D, HOOK, SPLIT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const int ncb = (p.m_end - p.m_begin + CTA_ROWS - 1) / CTA_ROWS;
-  dim3 grid(ncb, p.Hq, p.B);
-  tc_fwd_kernel<T, D, HOOK><<<grid, NTHREADS, L::alloc, s>>>(maps, p, device_status_word());
+  const int ncb = (p.m_end - p.m_begin + L::kRows - 1) / L::kRows;
+  FwdParams pp = p;
+  // K and V of all heads together stay resident in the 126 MB L2 -> order CTAs for load balance
+  const long long kv_bytes = 2LL * p.B * p.Hk * p.N * p.D * 2;
+  pp.lpt_order = (p.causal && kv_bytes <= (48LL << 20) && ncb <= 65535) ? 1 : 0;
+  dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, ncb) : dim3(ncb, p.Hq, p.B);
+  tc_fwd_kernel<T, D, HOOK, SPLIT><<<grid, NTHREADS, L::alloc, s>>>(maps, pp, device_status_word());
   count_launch();
   return cudaGetLastError();
+}
+
+// Few CTAs (less than two per SM with 256-row CTAs): the launch is bound by the longest chain of
+// dependent key tiles, so use 128-row CTAs whose two warpgroups split the key tiles.
+// FAWS_SPLIT_KV=0/1 in the environment overrides the choice (tests, ablations).
+bool use_split_kv(const FwdParams& p) {
+  static const int forced = [] {
+    const char* e = std::getenv("FAWS_SPLIT_KV");
+    return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+  }();
+  if (forced >= 0) return forced == 1;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long ctas256 = (long long)((p.m_end - p.m_begin + 255) / 256) * p.Hq * p.B;
+  return ctas256 < 2LL * sms;
+}
+
+template <typename T, int D, int HOOK>
+cudaError_t launch_fwd_h(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
+  return use_split_kv(p) ? launch_fwd_s<T, D, HOOK, true>(maps, p, s) : launch_fwd_s<T, D, HOOK, false>(maps, p, s);
 }
 
 template <typename T, int D>
@@ -1040,6 +1159,9 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
 }
 
 #ifdef FAWS_TRACE
+extern "C" int faws_debug_read_cta_times(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_cta_times, sizeof(long long) * n);
+}
 extern "C" int faws_debug_read_trace(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
 }
