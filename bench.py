@@ -200,10 +200,13 @@ def run_reference(args, rank):
 
 
 def time_op(fn, iters, warmup):
+    """Median CUDA-event time of one call, with the stream kept busy (a spin kernel is queued first) so
+    that host enqueue latency is not inside the event pairs."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    torch.cuda._sleep(int(2e6))
     for a, b in evs:
         a.record()
         fn()
