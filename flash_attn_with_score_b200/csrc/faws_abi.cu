@@ -98,8 +98,10 @@ int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, float* final_out,
     c.out = final_out;
     e = launch_scratch_colsum(c, group_sum, s);
   } else if (use_tc) {
-    c.out = final_out;
-    e = launch_tc_colsoftmax(c, p->dtype, group_sum, s);
+    const bool in_kernel = !group_sum || tc_colsoftmax_group_in_kernel(c);
+    c.out = in_kernel ? final_out : per_head_ws;
+    e = launch_tc_colsoftmax(c, p->dtype, in_kernel ? group_sum : 0, s);
+    if (e == cudaSuccess && !in_kernel) e = launch_group_sum(per_head_ws, final_out, c.B, c.Hk, c.G, c.n_end, s);
   } else {
     const bool direct = !group_sum || c.G == 1;
     c.out = direct ? final_out : per_head_ws;

@@ -86,6 +86,7 @@ cudaError_t launch_reduce_ranks(const float* parts, int n_ranks, int64_t count, 
 bool tc_fwd_supported(const FwdParams& p, int dtype);
 cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype);
+bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p);
 cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, int group_sum, cudaStream_t s);
 
 int tc_read_status(int reset);  // synchronising read of the device status word

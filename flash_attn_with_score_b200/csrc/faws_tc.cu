@@ -802,8 +802,12 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
   float* comb = reinterpret_cast<float*>(smem + L::comb_off);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN;
-  const int ho = blockIdx.y, b = blockIdx.z;
+  // Causal: key tiles are the slowest grid dimension, so the key tiles that see the most queries
+  // (the first ones) of all heads are dispatched first.  Otherwise key tiles are fastest.
+  const int n0 = (p.causal ? blockIdx.z : blockIdx.x) * BN;
+  const int ho = p.causal ? blockIdx.x : blockIdx.y;
+  const int b = p.causal ? blockIdx.y : blockIdx.z;
+  const int n_heads_out = p.causal ? gridDim.x : gridDim.y;
   const int h0 = ho * heads_per_cta;  // first query head of this CTA
   const int hk = h0 / p.G;
 
@@ -964,7 +968,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
   if (warp >= 4 && warp < 8) {
     const int row = (warp & 3) * 32 + lane;
     const int j = n0 + row;
-    if (j < p.n_end) p.out[((int64_t)b * gridDim.y + ho) * p.n_end + j] = acc + comb[row];
+    if (j < p.n_end) p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = acc + comb[row];
   }
   if (*abort_flag) {
     if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
@@ -1176,6 +1180,17 @@ int tc_read_status(int reset) {
   return v;
 }
 
+// Whether the kernel should walk the G heads of a kv head inside one CTA (output already group
+// summed) or run one CTA per query head followed by a group-sum kernel.  The latter gives G times
+// more CTAs, which matters for causal problems where the key tiles' work is very uneven.
+bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p) {
+  if (p.G == 1) return true;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long ctas = (long long)((p.n_end + BN - 1) / BN) * p.Hk * p.B;
+  return !(p.causal && ctas < 8LL * sms) && ctas >= 2LL * sms;
+}
+
 bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype) {
   (void)dtype;
   if (p.D != 64 && p.D != 128) return false;
@@ -1197,7 +1212,8 @@ cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  dim3 grid((p.n_end + BN - 1) / BN, p.Hq / heads_per_cta, p.B);
+  const int nkt = (p.n_end + BN - 1) / BN;
+  dim3 grid = p.causal ? dim3(p.Hq / heads_per_cta, p.B, nkt) : dim3(nkt, p.Hq / heads_per_cta, p.B);
   tc_colsoftmax_kernel<T, D><<<grid, NTHREADS, L::alloc, s>>>(maps, p, heads_per_cta, device_status_word());
   count_launch();
   return cudaGetLastError();
