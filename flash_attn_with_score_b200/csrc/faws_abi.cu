@@ -68,6 +68,7 @@ int run_fwd(const faws_problem* p, FwdParams& f, cudaStream_t s, int* block_m, i
   bool use_tc = false;
   if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_fwd_supported(f, p->dtype);
   if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
+  if (!use_tc) f.col_lin = 0;
   *block_m = use_tc ? kTcBlockM : kGenericBlockM;
   *block_n = use_tc ? kTcBlockN : kGenericBlockN;
   if (f.col_partial != nullptr) {
@@ -115,6 +116,9 @@ int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, float* final_out,
   return FAWS_OK;
 }
 
+// per-128-row-tile sums of the query rows, (B,Hq,ceil(M/128),128) floats
+size_t qsum_floats(const faws_problem* p) { return (size_t)p->B * p->Hq * cdiv(p->M, 128) * 128; }
+
 size_t partial_floats(const faws_problem* p, int row_begin, int n_end) {
   const int first = (row_begin > p->m_begin ? row_begin : p->m_begin) / kGenericBlockM;
   int nqb = cdiv(p->m_end, kGenericBlockM) - first;
@@ -128,24 +132,31 @@ int raw_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws
   int st = validate(p);
   if (st != FAWS_OK) return st;
   if (sum_out == nullptr) return FAWS_EINVAL;
-  const size_t need = align256(partial_floats(p, row_begin, n_end) * 4);
-  if (need > 0 && (ws == nullptr || ws_bytes < need)) return FAWS_EWORKSPACE;
+  const size_t part_bytes = align256(partial_floats(p, row_begin, n_end) * 4);
+  const size_t need = part_bytes + align256(qsum_floats(p) * 4);
+  if (ws == nullptr || ws_bytes < need) return FAWS_EWORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   FwdParams f = make_fwd(p);
   f.schedule = schedule;
   f.col_partial = static_cast<float*>(ws);
   f.col_row_begin = row_begin;
   f.col_n_end = n_end;
+  f.col_lin = 1;  // cleared by run_fwd when the CUDA-core kernels run
+  f.col_row_lo = row_begin > p->m_begin ? row_begin : p->m_begin;
+  float* qsum = reinterpret_cast<float*>(static_cast<char*>(ws) + part_bytes);
   int bm = 0, bn = 0;
   st = run_fwd(p, f, s, &bm, &bn);
   if (st != FAWS_OK) return st;
+  if (f.col_lin && launch_qtile_sums(f, p->dtype, qsum, s) != cudaSuccess) return FAWS_ECUDA;
   ReducePartialParams r{};
   r.partial = f.col_partial; r.out = sum_out;
   r.B = p->B; r.Hq = p->Hq; r.Hk = p->Hk; r.G = p->Hq / p->Hk; r.per_q_head = per_q_head ? 1 : 0;
   r.n_end = n_end; r.ncols_pad = f.ncols_pad; r.n_qb_part = f.n_qb_part; r.qb_first = f.qb_first;
   r.block_m = bm; r.block_n = bn;
   r.causal = f.causal; r.p_seq = f.p_seq; r.N = p->N; r.m_end = p->m_end;
-  if (launch_reduce_partials(r, s) != cudaSuccess) return FAWS_ECUDA;
+  r.lin = f.col_lin; r.qsum = qsum; r.nqb_total = cdiv(p->M, 128); r.D = p->D; r.row_lo = f.col_row_lo;
+  r.k = f.k; r.k_sb = f.k_sb; r.k_sh = f.k_sh; r.k_ss = f.k_ss; r.sm_scale = f.sm_scale;
+  if (launch_reduce_partials(r, p->dtype, s) != cudaSuccess) return FAWS_ECUDA;
   return FAWS_OK;
 }
 
@@ -297,10 +308,10 @@ size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split) {
   switch (op) {
     case FAWS_OP_COL_SUM:
     case FAWS_OP_COL_SUM_SEQUENTIAL:
-      return align256(partial_floats(p, 0, p->N) * 4);
+      return align256(partial_floats(p, 0, p->N) * 4) + align256(qsum_floats(p) * 4);
     case FAWS_OP_CROSS_QK_SUM:
       if (split <= 0 || split > p->N) return 0;
-      return align256(partial_floats(p, split, split) * 4);
+      return align256(partial_floats(p, split, split) * 4) + align256(qsum_floats(p) * 4);
     case FAWS_OP_SOFTMAX_COL_SUM:
       return carve_softmax_ws(p, nullptr, p->N, 0).total;
     case FAWS_OP_CROSS_SOFTMAX_SUM:

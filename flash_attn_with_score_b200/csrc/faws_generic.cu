@@ -414,6 +414,114 @@ __global__ void reduce_partials_kernel(ReducePartialParams p) {
   p.out[((int64_t)b * Hout + ho) * p.n_end + j] = sum;
 }
 
+// qsum[b,h,qb,d] = sum over the rows of query tile qb (128 rows from row 0) of q[b,h,row,d]
+template <typename T>
+__global__ void __launch_bounds__(128) qtile_sum_kernel(const T* q, int64_t sb, int64_t sh, int64_t ss, float* qsum,
+                                                        int Hq, int M, int D, int nqb_total) {
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (d < D) {
+    const T* base = q + b * sb + h * sh + d;
+    const int r0 = qb * 128, r1 = min(r0 + 128, M);
+    int r = r0;
+    for (; r + 3 < r1; r += 4) {
+      s0 += to_f(base[(int64_t)r * ss]);
+      s1 += to_f(base[(int64_t)(r + 1) * ss]);
+      s2 += to_f(base[(int64_t)(r + 2) * ss]);
+      s3 += to_f(base[(int64_t)(r + 3) * ss]);
+    }
+    for (; r < r1; ++r) s0 += to_f(base[(int64_t)r * ss]);
+  }
+  qsum[(((int64_t)b * Hq + h) * nqb_total + qb) * 128 + d] = (s0 + s1) + (s2 + s3);
+}
+
+// Column sums with the linear part: a block owns one 128-wide key tile t of one output head.
+// out[j] = sm_scale * sum_h k_j . V_h(t) + sum_h sum_{qb hooked} partial[h][qb][j], where
+// V_h(t) = sum of qsum[h][qb] over the query tiles for which col_tile_linear(qb, t) holds.
+template <typename T>
+__global__ void __launch_bounds__(128) reduce_colsum_lin_kernel(ReducePartialParams p) {
+  constexpr int LDK = 130;                 // padded row (elements): conflict-free column walks
+  __shared__ T Ks[128 * LDK];              // the key tile, loaded once and reused by every head
+  __shared__ float V[128];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int j = t * 128 + tid;
+  const int ho = blockIdx.y, b = blockIdx.z;
+  const int h0 = p.per_q_head ? ho : ho * p.G;
+  const int nh = p.per_q_head ? 1 : p.G;
+  const int Hout = p.per_q_head ? p.Hq : p.Hk;
+  const int hk = h0 / p.G;
+  const bool j_ok = j < p.n_end && j < p.N;
+  {
+    const T* kbase = reinterpret_cast<const T*>(p.k) + b * p.k_sb + hk * p.k_sh;
+    const bool vec = (reinterpret_cast<uintptr_t>(kbase) % 16 == 0) && (p.k_ss % 8 == 0);
+    const int chunks = p.D >> 3;  // 16-byte chunks per row
+    if (vec) {
+#pragma unroll 4
+      for (int idx = tid; idx < 128 * chunks; idx += 128) {
+        const int row = idx / chunks, c = idx - row * chunks;
+        const int jr = t * 128 + row;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (jr < p.N) w = *reinterpret_cast<const uint4*>(kbase + (int64_t)jr * p.k_ss + 8 * c);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&Ks[row * LDK + 8 * c]);
+        dst[0] = w.x; dst[1] = w.y; dst[2] = w.z; dst[3] = w.w;
+      }
+    } else {
+      for (int idx = tid; idx < 128 * p.D; idx += 128) {
+        const int row = idx / p.D, c = idx - row * p.D;
+        const int jr = t * 128 + row;
+        Ks[row * LDK + c] = jr < p.N ? kbase[(int64_t)jr * p.k_ss + c] : from_f<T>(0.f);
+      }
+    }
+  }
+  float lin_sum = 0.f, part_sum = 0.f;
+  for (int g = 0; g < nh; ++g) {
+    const int h = h0 + g;
+    float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+    if (tid < p.D) {
+      const float* qs = p.qsum + (((int64_t)b * p.Hq + h) * p.nqb_total) * 128 + tid;
+      int qb = 0;
+      for (; qb + 3 < p.nqb_total; qb += 4) {  // loads first, predicates after: four in flight
+        const float x0 = qs[(int64_t)qb * 128], x1 = qs[(int64_t)(qb + 1) * 128];
+        const float x2 = qs[(int64_t)(qb + 2) * 128], x3 = qs[(int64_t)(qb + 3) * 128];
+        v0 += col_tile_linear(qb, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x0 : 0.f;
+        v1 += col_tile_linear(qb + 1, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x1 : 0.f;
+        v2 += col_tile_linear(qb + 2, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x2 : 0.f;
+        v3 += col_tile_linear(qb + 3, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x3 : 0.f;
+      }
+      for (; qb < p.nqb_total; ++qb)
+        v0 += col_tile_linear(qb, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? qs[(int64_t)qb * 128] : 0.f;
+    }
+    __syncthreads();  // K tile loaded (first pass); previous head's V consumed
+    V[tid] = (v0 + v1) + (v2 + v3);
+    __syncthreads();
+    if (j_ok) {
+      float d0 = 0.f, d1 = 0.f;
+      const T* kr = &Ks[tid * LDK];
+#pragma unroll 8
+      for (int d = 0; d < p.D; d += 2) {
+        d0 = fmaf(to_f(kr[d]), V[d], d0);
+        d1 = fmaf(to_f(kr[d + 1]), V[d + 1], d1);
+      }
+      lin_sum += d0 + d1;
+      const float* base = p.partial + ((int64_t)(b * p.Hq + h) * p.n_qb_part) * p.ncols_pad + j;
+      float p0 = 0.f, p1 = 0.f;
+#pragma unroll 4
+      for (int qb = 0; qb < p.n_qb_part; ++qb) {
+        const int qa = p.qb_first + qb;
+        bool use = !col_tile_linear(qa, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq);  // else in lin_sum
+        if (p.causal) {
+          const int last = min((qa + 1) * p.block_m, p.m_end);
+          use = use && (t * 128 < min(p.N, p.p_seq + last));  // else the forward kernel never visited it
+        }
+        const float x = use ? base[(int64_t)qb * p.ncols_pad] : 0.f;
+        if (qb & 1) p1 += x; else p0 += x;
+      }
+      part_sum += p0 + p1;
+    }
+  }
+  if (j < p.n_end) p.out[((int64_t)b * Hout + ho) * p.n_end + j] = j_ok ? (p.sm_scale * lin_sum + part_sum) : 0.f;
+}
+
 __global__ void group_sum_kernel(const float* in, float* out, int Hk, int G, int len) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= len) return;
@@ -492,10 +600,29 @@ cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cuda
   return cudaGetLastError();
 }
 
-cudaError_t launch_reduce_partials(const ReducePartialParams& p, cudaStream_t s) {
+cudaError_t launch_reduce_partials(const ReducePartialParams& p, int dtype, cudaStream_t s) {
   if (p.n_end <= 0) return cudaSuccess;
-  dim3 grid((p.n_end + 255) / 256, p.per_q_head ? p.Hq : p.Hk, p.B);
-  reduce_partials_kernel<<<grid, 256, 0, s>>>(p);
+  if (p.lin) {
+    dim3 grid((p.n_end + 127) / 128, p.per_q_head ? p.Hq : p.Hk, p.B);
+    if (dtype == FAWS_FP16) reduce_colsum_lin_kernel<__half><<<grid, 128, 0, s>>>(p);
+    else reduce_colsum_lin_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p);
+  } else {
+    dim3 grid((p.n_end + 255) / 256, p.per_q_head ? p.Hq : p.Hk, p.B);
+    reduce_partials_kernel<<<grid, 256, 0, s>>>(p);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_qtile_sums(const FwdParams& p, int dtype, float* qsum, cudaStream_t s) {
+  const int nqb_total = (p.M + 127) / 128;
+  dim3 grid(nqb_total, p.Hq, p.B);
+  if (dtype == FAWS_FP16)
+    qtile_sum_kernel<__half><<<grid, 128, 0, s>>>(reinterpret_cast<const __half*>(p.q), p.q_sb, p.q_sh, p.q_ss, qsum,
+                                                  p.Hq, p.M, p.D, nqb_total);
+  else
+    qtile_sum_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(p.q), p.q_sb, p.q_sh,
+                                                         p.q_ss, qsum, p.Hq, p.M, p.D, nqb_total);
   count_launch();
   return cudaGetLastError();
 }

@@ -44,7 +44,22 @@ struct FwdParams {
   float* s_scratch;      // buffered variant: (B,Hq,M-split,split) scaled scores
   int split;
   int lpt_order;         // set by the tcgen05 launcher: heaviest causal row blocks of all heads first
+  int col_lin;           // column hook skips tiles that col_tile_linear() accepts (see below)
+  int col_row_lo;        // max(col_row_begin, m_begin): first query row that contributes
 };
+
+// Raw column sums are linear in q: for a 128 x 128 (query tile, key tile) pair in which every
+// entry is visible and every row contributes, sum_i s_ij = sm_scale * k_j . (sum_i q_i).  Such
+// pairs are not reduced inside the forward kernel; the reduce kernel adds them from per-tile sums
+// of the query rows.  Both sides use this one predicate.
+__host__ __device__ inline bool col_tile_linear(int qb, int t, int row_lo, int m_end, int N, int causal,
+                                                int p_seq) {
+  const int r0 = qb * 128;
+  if (r0 < row_lo || r0 + 128 > m_end) return false;
+  if (t * 128 + 128 > N) return false;
+  if (causal && t * 128 + 127 > r0 + p_seq) return false;
+  return true;
+}
 
 // Key-major softmax column-sum pass: out[b,h,j] = sum_{i>=i_begin, visible} exp(s_ij - L_i).
 struct ColSoftmaxParams {
@@ -70,13 +85,21 @@ struct ReducePartialParams {
   int n_end, ncols_pad, n_qb_part, qb_first;
   int block_m, block_n;  // tile sizes the forward kernel used
   int causal, p_seq, N, m_end;
+  // linear part (tcgen05 forward only; lin == 0 otherwise)
+  int lin;               // 1: add k_j . (sum of the query rows of the linear tiles)
+  const float* qsum;     // (B,Hq,nqb_total,128): per 128-row query tile, sum of its rows (fp32)
+  int nqb_total, D, row_lo;
+  const void* k;
+  int64_t k_sb, k_sh, k_ss;
+  float sm_scale;
 };
 
 // Launchers (each returns a cudaError_t from the launch).
 cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cudaStream_t s);
-cudaError_t launch_reduce_partials(const ReducePartialParams& p, cudaStream_t s);
+cudaError_t launch_reduce_partials(const ReducePartialParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_qtile_sums(const FwdParams& p, int dtype, float* qsum, cudaStream_t s);
 cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, int len,
                              cudaStream_t s);
 cudaError_t launch_reduce_ranks(const float* parts, int n_ranks, int64_t count, float* out,

@@ -427,6 +427,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 
     float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
     bool alive = true;
+    int hook_cnt = 0;  // column hook executions (selects its smem buffer and barrier phase)
 #ifdef FAWS_TRACE
     const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0);
     int tr_n = 0;
@@ -578,24 +579,32 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         }
       }
       if constexpr (HOOK == kHookColPart) {
-        const bool contrib = row_ok && i >= p.col_row_begin;
-        const int cbuf = cnt & 1;
+        // Tiles in which every entry is visible and every row contributes are left to the
+        // reduce kernel (column sums are linear in q there); only edge / diagonal tiles are
+        // reduced here.
+        const bool lin = p.col_lin != 0 &&
+                         col_tile_linear(qb128, n0 / BN, p.col_row_lo, p.m_end, p.N, p.causal, p.p_seq);
+        if (!lin) {
+          const bool contrib = row_ok && i >= p.col_row_begin;
+          const int cbuf = hook_cnt & 1;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float cv[32];
+          for (int c = 0; c < 4; ++c) {
+            float cv[32];
 #pragma unroll
-          for (int x = 0; x < 32; ++x)
-            cv[x] = (contrib && FAWS_VIS(c * 32 + x)) ? __uint_as_float(r[c * 32 + x]) * scale : 0.f;
-          warp_column_sums(cv, lane);
-          colbuf[(cbuf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
-        }
-        mbar_arrive(&bars->col_ready[qt]);
-        if (!mbar_wait(&bars->col_ready[qt], cnt & 1, abort_flag)) return false;
-        if (part_on && n0 + row < p.ncols_pad) {
-          const float* cb = colbuf + cbuf * 512;
-          // fixed order: the warps that own rows 0-31, 32-63, 64-95, 96-127
-          const float sum = ((cb[row] + cb[128 + row]) + cb[256 + row]) + cb[384 + row];
-          p.col_partial[((int64_t)bh * p.n_qb_part + (qb128 - p.qb_first)) * (int64_t)p.ncols_pad + n0 + row] = sum;
+            for (int x = 0; x < 32; ++x)
+              cv[x] = (contrib && FAWS_VIS(c * 32 + x)) ? __uint_as_float(r[c * 32 + x]) * scale : 0.f;
+            warp_column_sums(cv, lane);
+            colbuf[(cbuf * 4 + lg) * 128 + c * 32 + lane] = cv[0];
+          }
+          mbar_arrive(&bars->col_ready[qt]);
+          if (!mbar_wait(&bars->col_ready[qt], hook_cnt & 1, abort_flag)) return false;
+          ++hook_cnt;
+          if (part_on && n0 + row < p.ncols_pad) {
+            const float* cb = colbuf + cbuf * 512;
+            // fixed order: the warps that own rows 0-31, 32-63, 64-95, 96-127
+            const float sum = ((cb[row] + cb[128 + row]) + cb[256 + row]) + cb[384 + row];
+            p.col_partial[((int64_t)bh * p.n_qb_part + (qb128 - p.qb_first)) * (int64_t)p.ncols_pad + n0 + row] = sum;
+          }
         }
       }
 #undef FAWS_VIS
