@@ -612,6 +612,26 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       return true;
     };
 
+    // Key tiles the causal loop never visits hold only the fill value.  They are written first,
+    // from one constant 32 x 32 tile, so that HBM is busy while the first tiles are computed
+    // (these stores carry 44 % of the bytes of a causal S = N problem).
+    if constexpr (store_scores) if (r_tile < p.m_end && my_nt * BN < p.N) {
+      const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<float4*>(stage + lane * 128 + (cc << 4)) = fill;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int r0 = r_tile + lg * 32 - p.m_begin;
+        for (int j0 = my_nt * BN; j0 < p.N; j0 += 32) {
+          // SPLIT: the two warpgroups share the rows, so they take alternate key tiles
+          if (!SPLIT || ((j0 / BN) & 1) == qt) tma_store_3d(&maps.st, stage, j0, r0, bh);
+        }
+        tma_store_commit();
+      }
+      __syncwarp();
+    }
+
     {
       int cnt = 0;
       for (int it = 0; it < nt; ++it) {
@@ -717,23 +737,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if (p.L != nullptr)
           p.L[(int64_t)bh * p.M + i] = l_all > 0.f ? (m_all + log2f(l_all)) * kLn2 : FAWS_NEG_INF;
         if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs_all;
-      }
-    }
-    if constexpr (store_scores) if (alive && r_tile < p.m_end && my_nt * BN < p.N) {
-      if (lane < 2) tma_store_wait_read<0>();
-      __syncwarp();
-      const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<float4*>(stage + lane * 128 + (cc << 4)) = fill;
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        const int r0 = r_tile + lg * 32 - p.m_begin;
-        for (int j0 = my_nt * BN; j0 < p.N; j0 += 32) {
-          // SPLIT: the two warpgroups share the rows, so they take alternate key tiles
-          if (!SPLIT || ((j0 / BN) & 1) == qt) tma_store_3d(&maps.st, stage, j0, r0, bh);
-        }
-        tma_store_commit();
       }
     }
     TRACE(31);
