@@ -99,6 +99,7 @@ struct Bars {
   uint64_t q_full;
   uint64_t kv_full[MAX_KV_SLOTS], kv_empty[MAX_KV_SLOTS];
   uint64_t s_full[2];     // per query tile: S_t written by the tensor pipe
+  uint64_t p_half[2];     // per query tile: the first 64 columns of P_t are in TMEM
   uint64_t p_ready[2];    // per query tile: P_t written by its 128 softmax threads
   uint64_t col_ready[2];  // per query tile: column-sum partial rows of its 4 warps are in smem
   uint64_t o_done;        // every MMA of the CTA has completed
@@ -208,6 +209,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_half[t], 128);
       mbar_init(&bars->p_ready[t], 128);
       mbar_init(&bars->col_ready[t], 128);
     }
@@ -290,6 +292,33 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         __syncwarp();
       };
       // O_t (+)= P_t . V; P_t sits in the first 64 columns of S_t (two 16-bit values per column)
+      // The softmax hands P over in two halves of 64 key columns, so the first four K-steps of
+      // P.V run while the second half of the exponentials is still being computed.
+      auto issue_pv_half = [&](int t, int slot, bool accumulate, int half) {
+        const uint64_t vd = v_desc0 + (uint64_t)(slot * (L::kTile >> 4));
+        const uint32_t d_tmem = tmem_base + 256 + (uint32_t)(t * BN);
+        const uint32_t a_tmem = tmem_base + (uint32_t)(t * BN);
+        if (elect_one()) {
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const int kk = half * 4 + k4;
+            const uint64_t off = (uint64_t)((kk * 16 * 128) >> 4);
+            if (kk == 0) mma_ts(d_tmem, a_tmem, vd, idesc_pv, accumulate ? 1u : 0u);
+            else mma_ts_acc(d_tmem, a_tmem + (uint32_t)(kk * 8), vd + off, idesc_pv);
+          }
+        }
+        __syncwarp();
+      };
+      // waits for the two hand-offs of query tile / warpgroup t and issues both halves
+      auto pv_when_ready = [&](int t, int slot, int c) -> bool {
+        if (!mbar_wait(&bars->p_half[t], c & 1, abort_flag)) return false;
+        tc_fence_after();
+        issue_pv_half(t, slot, c > 0, 0);
+        if (!mbar_wait(&bars->p_ready[t], c & 1, abort_flag)) return false;
+        tc_fence_after();
+        issue_pv_half(t, slot, true, 1);
+        return true;
+      };
       auto issue_pv = [&](int t, int slot, bool accumulate) {
         const uint64_t vd = v_desc0 + (uint64_t)(slot * (L::kTile >> 4));
         const uint32_t d_tmem = tmem_base + 256 + (uint32_t)(t * BN);
@@ -330,9 +359,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           if (it >= 2) {
             const int v_idx = 2 * (it - 2) + 1;
             if (!(ok = kv_wait(v_idx))) break;
-            if (!(ok = mbar_wait(&bars->p_ready[w], cnt[w] & 1, abort_flag))) break;
-            tc_fence_after();
-            issue_pv(w, v_idx % KV_SLOTS, cnt[w] > 0);
+            if (!(ok = pv_when_ready(w, v_idx % KV_SLOTS, cnt[w]))) break;
             ++cnt[w];
             commit(&bars->kv_empty[v_idx % KV_SLOTS]);
           }
@@ -360,10 +387,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if (!(ok = kv_wait(2 * it + 1))) break;
         TRACE(11);
         if (tk < nt_q[0]) {
-          if (!(ok = mbar_wait(&bars->p_ready[0], cnt[0] & 1, abort_flag))) break;
+          if (!(ok = pv_when_ready(0, v_slot, cnt[0]))) break;
           TRACE(12);
-          tc_fence_after();
-          issue_pv(0, v_slot, cnt[0] > 0);
           ++cnt[0];
         }
         if (more) {
@@ -372,10 +397,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           if (tk_next < nt_q[0]) issue_qk(0, k_slot);
         }
         if (tk < nt_q[1]) {
-          if (!(ok = mbar_wait(&bars->p_ready[1], cnt[1] & 1, abort_flag))) break;
+          if (!(ok = pv_when_ready(1, v_slot, cnt[1]))) break;
           TRACE(14);
-          tc_fence_after();
-          issue_pv(1, v_slot, cnt[1] > 0);
           ++cnt[1];
         }
         commit(&bars->kv_empty[v_slot]);
@@ -514,6 +537,11 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           pk[g * 4 + 3] = pack2<T>(e[6], e[7]);
         }
         tmem_st16(t_s + c * 16, pk);
+        if (c == 1) {  // first 64 key columns of P are complete: let their P.V K-steps start
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&bars->p_half[qt]);
+        }
       }
       TRACE(24);
       tmem_wait_st();
