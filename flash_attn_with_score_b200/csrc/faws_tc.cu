@@ -56,6 +56,9 @@ static_assert(128 * REGS_AUX + 256 * REGS_SOFTMAX <= REGS_LAUNCH * NTHREADS, "se
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef FAWS_F32X2
+#define FAWS_F32X2 1
+#endif
 #define FAWS_NEG_INF (__int_as_float(0xff800000))
 
 #ifdef FAWS_TRACE
@@ -515,12 +518,30 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       // ---- P = exp2(s*scale*log2e - m), row sum of P, P -> TMEM over S as 16-bit pairs
       const float neg_m = (m_run == FAWS_NEG_INF) ? 0.f : -m_run;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#if FAWS_F32X2
+      const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
+      const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+      uint64_t lp0 = 0ull, lp1 = 0ull;
+#endif
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float e[8];
+#if FAWS_F32X2
+          // packed 2 x fp32 FMA / ADD: half the FMA-pipe instructions of the scalar form
+#pragma unroll
+          for (int y = 0; y < 8; y += 2) {
+            const int x = c * 32 + g * 8 + y;
+            float t0, t1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2, neg_m2), t0, t1);
+            e[y] = FAWS_VIS(x) ? fast_exp2(t0) : 0.f;
+            e[y + 1] = FAWS_VIS(x + 1) ? fast_exp2(t1) : 0.f;
+          }
+          lp0 = add_f32x2(lp0, add_f32x2(pack_f32x2(e[0], e[1]), pack_f32x2(e[4], e[5])));
+          lp1 = add_f32x2(lp1, add_f32x2(pack_f32x2(e[2], e[3]), pack_f32x2(e[6], e[7])));
+#else
 #pragma unroll
           for (int y = 0; y < 8; ++y) {
             const int x = c * 32 + g * 8 + y;
@@ -531,6 +552,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           l1 += e[1] + e[5];
           l2 += e[2] + e[6];
           l3 += e[3] + e[7];
+#endif
           pk[g * 4 + 0] = pack2<T>(e[0], e[1]);
           pk[g * 4 + 1] = pack2<T>(e[2], e[3]);
           pk[g * 4 + 2] = pack2<T>(e[4], e[5]);
@@ -545,6 +567,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
       TRACE(24);
       tmem_wait_st();
+#if FAWS_F32X2
+      unpack_f32x2(lp0, l0, l1);
+      unpack_f32x2(lp1, l2, l3);
+#endif
       l_run += (l0 + l1) + (l2 + l3);
       tc_fence_before();
       mbar_arrive(&bars->p_ready[qt]);
@@ -978,6 +1004,23 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       const bool full = !p.causal || (n0 + BN - 1 - p.p_seq - i0 <= 0);
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
       if (full) {
+#if FAWS_F32X2
+        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+        uint64_t ap0 = 0ull, ap1 = 0ull;
+#pragma unroll
+        for (int x = 0; x < 128; x += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(lb + x);
+          float t0, t1, t2, t3;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2,
+                                 pack_f32x2(nl.x, nl.y)), t0, t1);
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3])), scale2,
+                                 pack_f32x2(nl.z, nl.w)), t2, t3);
+          ap0 = add_f32x2(ap0, pack_f32x2(fast_exp2(t0), fast_exp2(t1)));
+          ap1 = add_f32x2(ap1, pack_f32x2(fast_exp2(t2), fast_exp2(t3)));
+        }
+        unpack_f32x2(ap0, a0, a1);
+        unpack_f32x2(ap1, a2, a3);
+#else
 #pragma unroll
         for (int x = 0; x < 128; x += 4) {
           const float4 nl = *reinterpret_cast<const float4*>(lb + x);
@@ -986,6 +1029,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           a2 += fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z));
           a3 += fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w));
         }
+#endif
       } else {
 #pragma unroll
         for (int x = 0; x < 128; x += 4) {
