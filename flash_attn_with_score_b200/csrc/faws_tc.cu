@@ -979,6 +979,10 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 
     bool alive = true;
     int mine = 0;  // tiles this warpgroup has processed
+#ifdef FAWS_TRACE
+    long long cs_wait_l = 0, cs_wait_s = 0, cs_ld = 0, cs_comp = 0, cs_pre = 0; int cs_tiles = 0;
+    const long long cs_t0 = clock64();
+#endif
     float negl_next = (wg < total) ? load_negl(wg) : FAWS_NEG_INF;
     for (int u = wg; u < total; u += 2, ++mine) {
       const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
@@ -986,8 +990,18 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       lb[row] = negl_next;  // slot s was last read by this warpgroup two tiles ago (before its l_ready wait)
       mbar_arrive(&bars->l_ready[wg]);
       if (u + 2 < total) negl_next = load_negl(u + 2);
+#ifdef FAWS_TRACE
+      const long long cw0 = clock64();
+#endif
       if (!mbar_wait(&bars->l_ready[wg], mine & 1, abort_flag)) { alive = false; break; }
+#ifdef FAWS_TRACE
+      const long long cw1 = clock64();
+#endif
       if (!mbar_wait(&bars->s_full[s], use & 1, abort_flag)) { alive = false; break; }
+#ifdef FAWS_TRACE
+      const long long cw2 = clock64();
+      cs_wait_l += cw1 - cw0; cs_wait_s += cw2 - cw1; ++cs_tiles;
+#endif
       tc_fence_after();
       uint32_t r[128];
 #pragma unroll
@@ -996,6 +1010,10 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&bars->s_free[s]);
+#ifdef FAWS_TRACE
+      const long long cw3 = clock64();
+      cs_ld += cw3 - cw2;
+#endif
 
       const int g = u / ntq, qt = qt0 + (u - g * ntq);
       const int i0 = qt * BM;
@@ -1041,7 +1059,17 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
         }
       }
       acc += (a0 + a1) + (a2 + a3);
+#ifdef FAWS_TRACE
+      cs_comp += clock64() - cw3;
+#endif
     }
+#ifdef FAWS_TRACE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0) {
+      long long* o = g_trace + 2 * 4096 + 4020 + wg * 4;
+      o[0] = cs_wait_l; o[1] = cs_wait_s; o[2] = cs_tiles; o[3] = clock64() - cs_t0;
+      g_trace[2 * 4096 + 4030 + wg * 2] = cs_ld; g_trace[2 * 4096 + 4031 + wg * 2] = cs_comp;
+    }
+#endif
     if (!alive) acc = 0.f;
     if (wg == 1) comb[row] = acc;
   }
