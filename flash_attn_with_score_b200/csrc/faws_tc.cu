@@ -121,6 +121,13 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <typename T> __device__ __forceinline__ uint32_t pack_bits(T lo, T hi) {
+  return (uint32_t)(*reinterpret_cast<const uint16_t*>(&lo)) | ((uint32_t)(*reinterpret_cast<const uint16_t*>(&hi)) << 16);
+}
+
 // In-warp transpose-reduce: on entry lane L holds v[0..31] (its row, 32 columns); on exit
 // v[0] of lane c is the sum over the 32 lanes of their v[c].  31 shuffles.
 __device__ __forceinline__ void warp_column_sums(float (&v)[32], int lane) {
@@ -137,7 +144,10 @@ __device__ __forceinline__ void warp_column_sums(float (&v)[32], int lane) {
 }
 
 // Score-tile hook compiled into a kernel instance (one per operator family).
-enum Hook : int { kHookNone = 0, kHookScores = 1, kHookRowSum = 2, kHookColPart = 3, kHookScratch = 4 };
+enum Hook : int {
+  kHookNone = 0, kHookScores = 1, kHookRowSum = 2, kHookColPart = 3, kHookScratch = 4,
+  kHookScores16 = 5  // scores in the input dtype (what the reference kernel writes)
+};
 
 template <typename T, int D, int HOOK, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -446,6 +456,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     unsigned char* stage = smem + L::stage_off + (warp - 4) * 8192;
     float* colbuf = reinterpret_cast<float*>(smem + L::stage_off + qt * 32768);  // [2][4][128], col hook only
     constexpr bool store_scores = HOOK == kHookScores;
+    constexpr bool store_scores16 = HOOK == kHookScores16;
     constexpr bool store_scratch = HOOK == kHookScratch;
     const int qb128 = r_tile / BM;
     const bool part_on = HOOK == kHookColPart && qb128 >= p.qb_first && r_tile < p.m_end;
@@ -588,6 +599,39 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         }
         rs_raw += (s0 + s1) + (s2 + s3);
       }
+      if constexpr (store_scores16) {
+        // 16-bit scores: a 64-column half tile is one 32-row x 128-byte box; the two 4 KB staging
+        // buffers alternate, lane 0 issues the stores.
+        const T masked_t = from_float<T>(masked_f);
+        const uint32_t masked2 = pack_bits<T>(masked_t, masked_t);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          unsigned char* sb = stage + half * 4096;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e2 = 0; e2 < 4; ++e2) {
+              const int x = half * 64 + cc * 8 + e2 * 2;
+              w[e2] = pack2<T>(__uint_as_float(r[x]) * scale, __uint_as_float(r[x + 1]) * scale);
+              if (kMasked) {
+                const bool v0 = x < nvis, v1 = x + 1 < nvis;
+                if (!v0 && !v1) w[e2] = masked2;
+                else if (!v1) w[e2] = (w[e2] & 0xffffu) | (masked2 & 0xffff0000u);
+              }
+            }
+            *reinterpret_cast<uint4*>(sb + lane * 128 + ((cc ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&maps.st, sb, n0 + half * 64, r_tile + lg * 32 - p.m_begin, bh);
+            tma_store_commit();
+          }
+        }
+      }
       if constexpr (store_scores || store_scratch) {
         // Two rounds of two 32-column chunks: both 4 KB staging buffers are rewritten per round,
         // one proxy fence per round, lanes 0 and 1 each issue (and later wait for) one TMA store.
@@ -679,6 +723,24 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const int r0 = r_tile + lg * 32 - p.m_begin;
         for (int j0 = my_nt * BN; j0 < p.N; j0 += 32) {
           // SPLIT: the two warpgroups share the rows, so they take alternate key tiles
+          if (!SPLIT || ((j0 / BN) & 1) == qt) tma_store_3d(&maps.st, stage, j0, r0, bh);
+        }
+        tma_store_commit();
+      }
+      __syncwarp();
+    }
+
+    if constexpr (store_scores16) if (r_tile < p.m_end && my_nt * BN < p.N) {
+      const T masked_t = from_float<T>(masked_f);
+      const uint32_t m2 = pack_bits<T>(masked_t, masked_t);
+      const uint4 fill = make_uint4(m2, m2, m2, m2);
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(stage + lane * 128 + (cc << 4)) = fill;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int r0 = r_tile + lg * 32 - p.m_begin;
+        for (int j0 = my_nt * BN; j0 < p.N; j0 += 64) {
           if (!SPLIT || ((j0 / BN) & 1) == qt) tma_store_3d(&maps.st, stage, j0, r0, bh);
         }
         tma_store_commit();
@@ -1131,15 +1193,16 @@ bool make_map_bhsd(CUtensorMap* m, const void* base, int D, int rows, int H, int
 }
 
 // 32 x 32 fp32 boxes into a (BH, rows, cols) tensor whose rows are `row_stride` floats apart
+// (esize = 2: 32-row x 64-column boxes of 16-bit elements, same 128-byte box rows)
 bool make_map_store_f32(CUtensorMap* m, void* base, int cols, int rows, int64_t row_stride,
-                        int64_t bh_stride, int BH) {
+                        int64_t bh_stride, int BH, int esize = 4) {
   EncodeTiledFn enc = get_encode();
   if (enc == nullptr) return false;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)bh_stride * 4};
-  cuuint32_t box[3] = {32, 32, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride * esize, (cuuint64_t)bh_stride * esize};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / esize), 32, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr,
+  CUresult r = enc(m, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -1219,7 +1282,8 @@ cudaError_t launch_fwd_h(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
 
 template <typename T, int D>
 cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
-  if (p.scores != nullptr) return launch_fwd_h<T, D, kHookScores>(maps, p, s);
+  if (p.scores != nullptr)
+    return p.scores_f32 ? launch_fwd_h<T, D, kHookScores>(maps, p, s) : launch_fwd_h<T, D, kHookScores16>(maps, p, s);
   if (p.row_sum != nullptr) return launch_fwd_h<T, D, kHookRowSum>(maps, p, s);
   if (p.col_partial != nullptr) return launch_fwd_h<T, D, kHookColPart>(maps, p, s);
   if (p.s_scratch != nullptr) return launch_fwd_h<T, D, kHookScratch>(maps, p, s);
@@ -1237,8 +1301,8 @@ bool tc_fwd_supported(const FwdParams& p, int dtype) {
   if (!ok16(p.q, p.q_sb, p.q_sh, p.q_ss) || !ok16(p.k, p.k_sb, p.k_sh, p.k_ss) ||
       !ok16(p.v, p.v_sb, p.v_sh, p.v_ss) || !ok16(p.o, p.o_sb, p.o_sh, p.o_ss))
     return false;
-  if (p.scores != nullptr) {
-    if (!p.scores_f32 || p.N % 4 != 0 || reinterpret_cast<uintptr_t>(p.scores) % 16 != 0) return false;
+  if (p.scores != nullptr) {  // TMA store rows must start on 16-byte boundaries
+    if (p.N % (p.scores_f32 ? 4 : 8) != 0 || reinterpret_cast<uintptr_t>(p.scores) % 16 != 0) return false;
   }
   if (p.s_scratch != nullptr) {
     if (p.scores != nullptr) return false;
@@ -1259,8 +1323,9 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
   if (!make_map_bhsd(&maps.o, obase, p.D, q_rows, p.Hq, p.B, p.o_ss, p.o_sh, p.o_sb, 32)) return cudaErrorInvalidValue;
   maps.st = maps.q;
   if (p.scores != nullptr) {
-    float* base = static_cast<float*>(p.scores) + (int64_t)p.m_begin * p.N;
-    if (!make_map_store_f32(&maps.st, base, p.N, q_rows, p.N, (int64_t)p.M * p.N, p.B * p.Hq))
+    const int esize = p.scores_f32 ? 4 : 2;
+    char* base = static_cast<char*>(p.scores) + (int64_t)p.m_begin * p.N * esize;
+    if (!make_map_store_f32(&maps.st, base, p.N, q_rows, p.N, (int64_t)p.M * p.N, p.B * p.Hq, esize))
       return cudaErrorInvalidValue;
   } else if (p.s_scratch != nullptr) {
     const int rows = p.m_end - p.split;  // rows of the cross region inside the window

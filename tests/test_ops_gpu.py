@@ -191,7 +191,8 @@ def test_kernel_golden_fixtures(golden_dir):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("causal", [True, False], ids=["causal", "full"])
 @pytest.mark.parametrize("shape", [(1, 2, 1, 256, 256, 128), (1, 2, 2, 200, 328, 64), (2, 6, 2, 640, 640, 128),
-                                   (1, 1, 1, 128, 1000, 128), (1, 2, 2, 1000, 1000, 64)],
+                                   (1, 1, 1, 128, 1000, 128), (1, 2, 2, 1000, 1000, 64), (1, 2, 1, 384, 128, 64),
+                                   (1, 4, 4, 300, 72, 128)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_tcgen05_family_is_used_and_matches(shape, causal, dtype):
     """Forces the tcgen05 kernels (an unsupported problem would raise) on aligned and ragged shapes."""
@@ -206,6 +207,16 @@ def test_tcgen05_family_is_used_and_matches(shape, causal, dtype):
     _check_out(o, ref_out, slack)
     ok, viol, ok_mask = orc.check_scores(s.cpu(), ref_scores)
     assert ok_mask and ok, viol
+    if N % 8 == 0:  # the reference kernel's own output format: q.dtype scores, 0 at hidden entries
+        o, s0 = F.attention_with_scores(qd, kd, vd, causal, scores_dtype=dtype, masked_value=0.0, **kw)
+        assert F.last_backend() == "tcgen05"
+        _check_out(o, ref_out, slack)
+        zref = torch.where(torch.isneginf(ref_scores), torch.zeros_like(ref_scores), ref_scores)
+        tol = 4e-3 if dtype == torch.float16 else 3e-2
+        assert s0.dtype == dtype and (s0.float().cpu() - zref).abs().max() < tol * max(1.0, zref.abs().max().item())
+        assert bool((s0.cpu()[torch.isneginf(ref_scores)] == 0).all())
+        o, s1 = F.attention_with_scores(qd, kd, vd, causal, scores_dtype=dtype, **kw)
+        assert torch.equal(torch.isneginf(s1.cpu()), torch.isneginf(ref_scores))
     o, L, _, _, _ = F.attention(qd, kd, vd, causal, return_log_normalizer=True, **kw)
     _check_out(o, ref_out, slack)
     Lref = orc.log_normalizer(ref_scores)
