@@ -229,7 +229,7 @@ def ops_table(F, device, pk):
         ("cfg4", cfg4, 3072, [("cross_qk", F.attention_cross_token_qk_sum),
                               ("cross_softmax", F.attention_cross_token_softmax_sum),
                               ("cross_softmax_buffered", F.attention_cross_token_softmax_sum_buffered)]),
-        ("cfg5", cfg5, None, [("softmax_col_sum", F.attention_with_softmax_col_sum)]),
+        ("cfg5", cfg5, None, [("attention", F.attention), ("softmax_col_sum", F.attention_with_softmax_col_sum)]),
         ("cfg5", cfg5, 12288, [("cross_softmax", F.attention_cross_token_softmax_sum)]),
     ]
     for name, cfg, split, ops in plans:
