@@ -37,7 +37,7 @@ sys.path.insert(0, ROOT)
 
 CFG2 = dict(B=1, Hq=32, Hk=32, S=1024, D=128, dtype=torch.float16, causal=True)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on this
-# workload, from the ncu capture summarised in profiles/tc_fwd_scores_cfg2.md (None = not captured)
+# workload, from the committed ncu summary of that kernel on this workload (None = not captured)
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 111_794_688  # 25.32 MB read + 86.47 MB written (the rest stays dirty in L2)
 N_SETS = 4  # rotating buffer sets: 4 x (134 MB scores + 8 MB out + 25 MB inputs) > 126 MB of L2
 
@@ -324,7 +324,6 @@ def main():
         dist.barrier()
     torch.cuda.synchronize()
     launches = F.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     total_ms = t_start.elapsed_time(t_end)
     step_event_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
     status = F.device_status()
@@ -378,6 +377,8 @@ def main():
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = te.item() / e2e_steps
+    # the sampler ran through the timed steps, the kernel-duration leg and the end-to-end leg
+    clocks = sampler.stop() if rank == 0 else None
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv))
     d2h = h_out.numel() * h_out.element_size() + h_scores.numel() * 4
 
