@@ -44,6 +44,7 @@ struct FwdParams {
   float* s_scratch;      // buffered variant: (B,Hq,M-split,split) scaled scores
   int split;
   int lpt_order;         // set by the tcgen05 launcher: heaviest causal row blocks of all heads first
+  int fill_ctas;         // set by the tcgen05 launcher: masked score tiles are written by extra CTAs
   int col_lin;           // column hook skips tiles that col_tile_linear() accepts (see below)
   int col_row_lo;        // max(col_row_begin, m_begin): first query row that contributes
 };

@@ -175,8 +175,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   // K/V through L2.  lpt_order (causal, K/V small enough to stay in L2 anyway): row blocks
   // slowest, so the heaviest row blocks of every head are dispatched first (longest-processing-
   // time-first packing of the causal triangle onto the SMs).
-  const int ncb = p.lpt_order ? gridDim.z : gridDim.x;
-  const int cb_rel = ncb - 1 - (int)(p.lpt_order ? blockIdx.z : blockIdx.x);  // heaviest (last) blocks first
+  // fill_ctas (score hooks, causal): the row-block axis holds two CTAs per row block, a compute
+  // CTA and a fill CTA that only writes the row block's never-visited key tiles; interleaved so
+  // that their costs decrease together (heaviest compute block, most-masked fill block, ...).
+  const int slot = (int)(p.lpt_order ? blockIdx.z : blockIdx.x);
+  const int ncb = (int)(p.lpt_order ? gridDim.z : gridDim.x) >> (p.fill_ctas ? 1 : 0);
+  const bool is_fill = p.fill_ctas && (slot & 1);
+  const int cb_slot = p.fill_ctas ? (slot >> 1) : slot;
+  const int cb_rel = is_fill ? cb_slot : ncb - 1 - cb_slot;  // heaviest (last) blocks first
   const int m0 = p.m_begin + cb_rel * CTA_ROWS;
   const int cb_abs = m0 / CTA_ROWS;
   const int h = p.lpt_order ? blockIdx.x : blockIdx.y;
@@ -197,6 +203,45 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     nt_q[t] = (hi + BN - 1) / BN;
   }
   const int nt = max(nt_q[0], nt_q[1]);
+
+  if constexpr (HOOK == kHookScores || HOOK == kHookScores16) {
+    if (is_fill) {
+      // Fill CTA: no barriers, no TMEM.  Every warp owns a constant 32-row x 128-byte tile and
+      // stores it over its share of the (32-row group, 128-byte column chunk) units.
+      constexpr int kCols = HOOK == kHookScores ? 32 : 64;  // elements per 128-byte chunk
+      unsigned char* tile = smem + warp * 4096;
+      const float masked_f = __uint_as_float(p.masked_bits);
+      uint32_t word = p.masked_bits;
+      if (HOOK == kHookScores16) {
+        const T mt = from_float<T>(masked_f);
+        word = pack_bits<T>(mt, mt);
+      }
+      const uint4 fill = make_uint4(word, word, word, word);
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(tile + lane * 128 + (cc << 4)) = fill;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        constexpr int kGroups = CTA_ROWS / 32;
+        int unit = 0;  // (row group, column chunk) units are dealt round-robin to the 12 warps
+        for (int rg = 0; rg < kGroups; ++rg) {
+          const int r0 = m0 + rg * 32;
+          if (r0 >= p.m_end) break;
+          const int t = SPLIT ? 0 : rg / 4;
+          for (int j0 = nt_q[t] * BN; j0 < p.N; j0 += kCols, ++unit) {
+            if (unit % 12 == warp) tma_store_3d(&maps.st, tile, j0, r0 - p.m_begin, bh);
+          }
+        }
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+#ifdef FAWS_TRACE
+      __syncthreads();
+      if (threadIdx.x == 0 && cta_lin < 4096) g_cta_times[cta_lin * 3 + 1] = gtimer();
+#endif
+      return;
+    }
+  }
 
   auto tile_of = [&](int it) -> int {
     if (p.schedule == kReverse) return nt - 1 - it;
@@ -713,7 +758,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     // Key tiles the causal loop never visits hold only the fill value.  They are written first,
     // from one constant 32 x 32 tile, so that HBM is busy while the first tiles are computed
     // (these stores carry 44 % of the bytes of a causal S = N problem).
-    if constexpr (store_scores) if (r_tile < p.m_end && my_nt * BN < p.N) {
+    if constexpr (store_scores) if (!p.fill_ctas && r_tile < p.m_end && my_nt * BN < p.N) {
       const float4 fill = make_float4(masked_f, masked_f, masked_f, masked_f);
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<float4*>(stage + lane * 128 + (cc << 4)) = fill;
@@ -730,7 +775,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       __syncwarp();
     }
 
-    if constexpr (store_scores16) if (r_tile < p.m_end && my_nt * BN < p.N) {
+    if constexpr (store_scores16) if (!p.fill_ctas && r_tile < p.m_end && my_nt * BN < p.N) {
       const T masked_t = from_float<T>(masked_f);
       const uint32_t m2 = pack_bits<T>(masked_t, masked_t);
       const uint4 fill = make_uint4(m2, m2, m2, m2);
@@ -1253,8 +1298,11 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   FwdParams pp = p;
   // K and V of all heads together stay resident in the 126 MB L2 -> order CTAs for load balance
   const long long kv_bytes = 2LL * p.B * p.Hk * p.N * p.D * 2;
-  pp.lpt_order = (p.causal && kv_bytes <= (48LL << 20) && ncb <= 65535) ? 1 : 0;
-  dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, ncb) : dim3(ncb, p.Hq, p.B);
+  pp.lpt_order = (p.causal && kv_bytes <= (48LL << 20) && 2 * ncb <= 65535) ? 1 : 0;
+  // masked key tiles exist (causal, some row block ends before N): give them their own CTAs
+  pp.fill_ctas = ((HOOK == kHookScores || HOOK == kHookScores16) && p.causal && p.p_seq + p.m_begin + 128 < p.N) ? 1 : 0;
+  const int nslots = pp.fill_ctas ? 2 * ncb : ncb;
+  dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, nslots) : dim3(nslots, p.Hq, p.B);
   tc_fwd_kernel<T, D, HOOK, SPLIT><<<grid, NTHREADS, L::alloc, s>>>(maps, pp, device_status_word());
   count_launch();
   return cudaGetLastError();
@@ -1277,7 +1325,12 @@ bool use_split_kv(const FwdParams& p) {
 
 template <typename T, int D, int HOOK>
 cudaError_t launch_fwd_h(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
-  return use_split_kv(p) ? launch_fwd_s<T, D, HOOK, true>(maps, p, s) : launch_fwd_s<T, D, HOOK, false>(maps, p, s);
+  // Score-materialising causal launches are bound by their stores, not by the chain of key
+  // tiles: measured, the 256-row CTAs (half as many set-ups) are faster there.
+  const bool store_bound = (HOOK == kHookScores || HOOK == kHookScores16) && p.causal;
+  static const bool forced = std::getenv("FAWS_SPLIT_KV") != nullptr;
+  const bool split = use_split_kv(p) && (forced || !store_bound);
+  return split ? launch_fwd_s<T, D, HOOK, true>(maps, p, s) : launch_fwd_s<T, D, HOOK, false>(maps, p, s);
 }
 
 template <typename T, int D>
