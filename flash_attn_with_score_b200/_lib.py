@@ -42,7 +42,8 @@ class Problem(C.Structure):
         ("m_begin", C.c_int32), ("m_end", C.c_int32),
         ("q", Tensor), ("k", Tensor), ("v", Tensor), ("out", Tensor),
         ("log_normalizer", C.c_void_p),
-        ("backend", C.c_int32), ("reserved", C.c_int32),
+        ("backend", C.c_int32), ("dropout_p", C.c_float), ("dropout_scale", C.c_float), ("reserved", C.c_int32),
+        ("philox_seed", C.c_uint64), ("philox_offset", C.c_uint64),
     ]
 
 

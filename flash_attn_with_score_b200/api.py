@@ -13,7 +13,10 @@ Deliberate differences, all keyword-only:
     reference kernels' group-summed (B,Hk,.) (attention_with_col_sum.py:72,370).
   * ``q_rows=(begin, end)`` restricts the call to a window of query rows (the
     query-split multi-GPU variant); ``backend`` forces a kernel family.
-  * ``dropout_p > 0`` raises NotImplementedError.
+  * ``dropout_p > 0`` draws the same mask as the reference kernels (Philox stream of
+    ``tl.rand(seed, offset + linear index, n_rounds=6)``, flash.py:376-380,463-466) with seed and
+    offset taken from, and advanced on, torch's CUDA generator exactly as dropout.py:5-15 does;
+    ``philox=(seed, offset)`` pins them instead.  Dropout problems run on the CUDA-core kernels.
 """
 from __future__ import annotations
 
@@ -41,11 +44,24 @@ def _stream(t):
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
+def philox_cuda_seed_offset(increment, device=None):
+    """(seed, offset) of the device's default CUDA generator; advances the offset by ``increment``
+    rounded up to a multiple of 4 (the bookkeeping of dropout.py:5-15)."""
+    device = torch.cuda.current_device() if device is None else torch.device(device).index
+    gen = torch.cuda.default_generators[device]
+    state = gen.get_state()
+    words = state.view(torch.int64)
+    seed, offset = int(words[0]), int(words[1])
+    words[1] += (increment + 3) // 4 * 4
+    gen.set_state(state)
+    return seed, offset
+
+
 class _Call:
     """Validated arguments + the faws_problem struct shared by every operator."""
 
     def __init__(self, q, k, v, causal, sm_scale, dropout_p, out=None, need_L=False, L=None,
-                 q_rows=None, backend=None, msgs=None):
+                 q_rows=None, backend=None, msgs=None, philox=None, rescale=False):
         m = msgs or {}
         Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
         assert Dq == Dk == Dv, m.get("D", "feature size of q, k, v should be equal")
@@ -56,8 +72,6 @@ class _Call:
         assert Hk == Hv, m.get("Hkv", "num of heads in k and v should be equal")
         assert H % Hk == 0, m.get("G", "number of heads in q must be a multiple of that in k & v")
         assert k.shape[0] == B and v.shape[0] == B and v.shape[2] == N
-        if dropout_p and dropout_p > 0.0:
-            raise NotImplementedError("dropout_p > 0 is not implemented by the B200 kernels")
         if not q.is_cuda:
             raise RuntimeError("flash_attn_with_score_b200 runs on CUDA tensors only (no CPU fallback)")
         if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
@@ -87,6 +101,20 @@ class _Call:
         p.q, p.k, p.v, p.out = _tensor(self.q), _tensor(self.k), _tensor(self.v), _tensor(self.out)
         p.log_normalizer = L.data_ptr() if L is not None else None
         p.backend = _lib.BACKENDS[backend]
+        self.seed = self.offset = None
+        if dropout_p and dropout_p > 0.0:
+            assert dropout_p < 1.0, "dropout_p must be < 1"
+            seed, offset = philox if philox is not None else philox_cuda_seed_offset(B * H * M * N, q.device)
+            if not 0 <= offset < 2 ** 31:
+                raise NotImplementedError("Philox offsets >= 2**31 select triton's 64-bit generator, "
+                                          "which is not implemented")
+            p.dropout_p = float(dropout_p)
+            # attention and attention_with_scores rescale by 1/(1-p) (flash.py:488-491,
+            # attention_with_scores.py:201-203); the reference's other operators only mask
+            p.dropout_scale = 1.0 / (1.0 - float(dropout_p)) if rescale else 1.0
+            p.philox_seed = seed & (2 ** 64 - 1)
+            p.philox_offset = offset
+            self.seed, self.offset = seed, offset
         self.p = p
 
     def workspace(self, op, split=0):
@@ -108,31 +136,34 @@ def _f32_bits(x: float) -> int:
 
 def attention(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
               return_log_normalizer=False, return_total_attention=False, return_seed_offset=False,
-              *, q_rows=None, backend=None):
+              *, q_rows=None, backend=None, philox=None):
     """FlashAttention forward; the reference's ``attention`` (flash.py:264-295), forward only.
 
     Returns ``out`` or, if any ``return_*`` flag is set, the reference's 5-tuple
     ``(out, log_normalizer|None, total_attention|None, seed|None, offset|None)``
     (flash.py:160-169)."""
     need_L = return_log_normalizer or return_total_attention
-    c = _Call(q, k, v, causal, sm_scale, dropout_p, need_L=need_L, q_rows=q_rows, backend=backend)
+    c = _Call(q, k, v, causal, sm_scale, dropout_p, need_L=need_L, q_rows=q_rows, backend=backend,
+              philox=philox, rescale=True)
     c.run("faws_attention")
     tot = None
     if return_total_attention:
         tot = torch.empty((c.B, c.H, c.N), device=c.dev, dtype=torch.float32)
         c.run("faws_total_attention", C.c_void_p(tot.data_ptr()))
     if return_log_normalizer or return_total_attention or return_seed_offset:
-        return (c.out, c.L if return_log_normalizer else None, tot, None, None)
+        return (c.out, c.L if return_log_normalizer else None, tot,
+                c.seed if return_seed_offset else None, c.offset if return_seed_offset else None)
     return c.out
 
 
 def attention_with_scores(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
                           *, scores_dtype=torch.float32, masked_value=float("-inf"),
-                          q_rows=None, backend=None, out=None, scores=None):
+                          q_rows=None, backend=None, out=None, scores=None, philox=None):
     """``(out, scores)`` with q.k^T computed once (attention_with_scores.py:214-333).
 
     scores: (B,Hq,M,N), ``scores_dtype`` (fp32 or q.dtype), hidden entries = ``masked_value``."""
-    c = _Call(q, k, v, causal, sm_scale, dropout_p, out=out, q_rows=q_rows, backend=backend)
+    c = _Call(q, k, v, causal, sm_scale, dropout_p, out=out, q_rows=q_rows, backend=backend,
+              philox=philox, rescale=True)
     if scores_dtype not in (torch.float32, q.dtype):
         raise TypeError("scores_dtype must be torch.float32 or q.dtype")
     if scores is None:
@@ -144,18 +175,20 @@ def attention_with_scores(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
     return c.out, scores
 
 
-def attention_with_row_sum(q, k, v, causal=False, sm_scale=None, dropout_p=0.0, *, q_rows=None, backend=None):
+def attention_with_row_sum(q, k, v, causal=False, sm_scale=None, dropout_p=0.0, *, q_rows=None, backend=None,
+                           philox=None):
     """``(out, row_sum)``; row_sum (B,Hq,M) fp32 = sum over visible keys of the scaled
     score (attention_with_row_sum.py:204-326)."""
-    c = _Call(q, k, v, causal, sm_scale, dropout_p, q_rows=q_rows, backend=backend)
+    c = _Call(q, k, v, causal, sm_scale, dropout_p, q_rows=q_rows, backend=backend, philox=philox)
     rs = torch.empty((c.B, c.H, c.M), device=c.dev, dtype=torch.float32)
     c.run("faws_attention_with_row_sum", C.c_void_p(rs.data_ptr()))
     return c.out, rs
 
 
 def _col_like(fn_name, op, q, k, v, causal, sm_scale, dropout_p, per_q_head, q_rows, backend,
-              split=None, out=None, sum_out=None, msgs=None):
-    c = _Call(q, k, v, causal, sm_scale, dropout_p, out=out, q_rows=q_rows, backend=backend, msgs=msgs)
+              split=None, out=None, sum_out=None, msgs=None, philox=None):
+    c = _Call(q, k, v, causal, sm_scale, dropout_p, out=out, q_rows=q_rows, backend=backend, msgs=msgs,
+              philox=philox)
     length = c.N if split is None else split
     heads = c.H if per_q_head else c.Hk
     if sum_out is None:
@@ -170,28 +203,28 @@ def _col_like(fn_name, op, q, k, v, causal, sm_scale, dropout_p, per_q_head, q_r
 
 
 def attention_with_col_sum(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
-                           *, per_q_head=False, q_rows=None, backend=None):
+                           *, per_q_head=False, q_rows=None, backend=None, philox=None):
     """``(out, col_sum)``; col_sum (B,Hk,N) fp32 = sum over visible queries (and the G query
     heads of the kv head) of the scaled score; reverse-order key tiles when causal
     (attention_with_col_sum.py:297-419).  Deterministic."""
     return _col_like("faws_attention_with_col_sum", _lib.OP_COL_SUM, q, k, v, causal, sm_scale,
-                     dropout_p, per_q_head, q_rows, backend)
+                     dropout_p, per_q_head, q_rows, backend, philox=philox)
 
 
 def attention_with_col_sum_sequential(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
-                                      *, per_q_head=False, q_rows=None, backend=None):
+                                      *, per_q_head=False, q_rows=None, backend=None, philox=None):
     """Same sums as ``attention_with_col_sum`` with round-robin key-tile order
     (attention_with_col_sum_sequential.py:214-341)."""
     return _col_like("faws_attention_with_col_sum_sequential", _lib.OP_COL_SUM_SEQUENTIAL, q, k, v,
-                     causal, sm_scale, dropout_p, per_q_head, q_rows, backend)
+                     causal, sm_scale, dropout_p, per_q_head, q_rows, backend, philox=philox)
 
 
 def attention_with_softmax_col_sum(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
-                                   *, per_q_head=False, q_rows=None, backend=None):
+                                   *, per_q_head=False, q_rows=None, backend=None, philox=None):
     """``(out, col_sum)``; column sums of the softmax weights
     (attention_with_col_softmax_sum.py:274-401)."""
     return _col_like("faws_attention_with_softmax_col_sum", _lib.OP_SOFTMAX_COL_SUM, q, k, v, causal,
-                     sm_scale, dropout_p, per_q_head, q_rows, backend)
+                     sm_scale, dropout_p, per_q_head, q_rows, backend, philox=philox)
 
 
 _XMSG = {"D": "Feature dimensions of q, k, v must be equal", "Hkv": "Number of heads in k and v must be equal",
@@ -200,7 +233,7 @@ _XMSG = {"D": "Feature dimensions of q, k, v must be equal", "Hkv": "Number of h
 
 def attention_cross_token_qk_sum(q, k, v, split, causal=False, sm_scale=None, dropout_p=0.0,
                                  *, out=None, cross_token_qk_out=None, reuse_buffers=False,
-                                 per_q_head=False, q_rows=None, backend=None):
+                                 per_q_head=False, q_rows=None, backend=None, philox=None):
     """``(out, cross_token_qk)``; cross_token_qk (B,Hk,split) fp32 = scaled-score sum from
     queries >= split into keys < split (attention_cross_token_qk_sum.py:255-408).
     ``out`` / ``cross_token_qk_out`` are optional caller-owned buffers (:341-357)."""
@@ -222,27 +255,28 @@ def attention_cross_token_qk_sum(q, k, v, split, causal=False, sm_scale=None, dr
         assert cross_token_qk_out.is_contiguous()
     return _col_like("faws_attention_cross_token_qk_sum", _lib.OP_CROSS_QK_SUM, q, k, v, causal, sm_scale,
                      dropout_p, per_q_head, q_rows, backend, split=split, out=out,
-                     sum_out=cross_token_qk_out, msgs=_XMSG)
+                     sum_out=cross_token_qk_out, msgs=_XMSG, philox=philox)
 
 
 def attention_cross_token_softmax_sum(q, k, v, split, causal=False, sm_scale=None, dropout_p=0.0,
-                                      *, per_q_head=False, q_rows=None, backend=None):
+                                      *, per_q_head=False, q_rows=None, backend=None, philox=None):
     """``(out, sums)``; sums (B,Hk,split) fp32 = softmax-weight sum from queries >= split into
     keys < split; second q.k^T over the cross region (attention_cross_token_softmax_sum.py:735-863)."""
     N = k.shape[2]
     assert 0 < split <= N, f"Split position must be in valid range (0, {N}]"
     return _col_like("faws_attention_cross_token_softmax_sum", _lib.OP_CROSS_SOFTMAX_SUM, q, k, v, causal,
-                     sm_scale, dropout_p, per_q_head, q_rows, backend, split=split)
+                     sm_scale, dropout_p, per_q_head, q_rows, backend, split=split, philox=philox)
 
 
 def attention_cross_token_softmax_sum_buffered(q, k, v, split, causal=False, sm_scale=None, dropout_p=0.0,
-                                               *, per_q_head=False, q_rows=None, backend=None):
+                                               *, per_q_head=False, q_rows=None, backend=None, philox=None):
     """Same sums as ``attention_cross_token_softmax_sum``; the first pass stores the cross
-    region's scores and the second reads them back (attention_cross_token_softmax_sum.py:639-732)."""
+    region's scores and the second reads them back (attention_cross_token_softmax_sum.py:639-732).
+    ``dropout_p`` is accepted and ignored, as in the reference (:646,713-730)."""
     N = k.shape[2]
     assert 0 < split <= N, f"Split position must be in valid range (0, {N}]"
     return _col_like("faws_attention_cross_token_softmax_sum_buffered", _lib.OP_CROSS_SOFTMAX_SUM_BUFFERED,
-                     q, k, v, causal, sm_scale, dropout_p, per_q_head, q_rows, backend, split=split)
+                     q, k, v, causal, sm_scale, 0.0, per_q_head, q_rows, backend, split=split)
 
 
 def total_attention(q, k, log_normalizer, causal=False, sm_scale=None, *, backend=None):

@@ -23,9 +23,23 @@ int validate(const faws_problem* p) {
   if (p->D != 16 && p->D != 32 && p->D != 64 && p->D != 128) return FAWS_EUNSUPPORTED;
   if (p->dtype != FAWS_FP16 && p->dtype != FAWS_BF16) return FAWS_EUNSUPPORTED;
   if (p->m_begin < 0 || p->m_end > p->M || p->m_begin > p->m_end) return FAWS_EINVAL;
+  if (!(p->dropout_p >= 0.f && p->dropout_p < 1.f)) return FAWS_EINVAL;
+  if (p->dropout_p > 0.f && p->philox_offset >= (1ull << 31)) return FAWS_EUNSUPPORTED;
   if (p->q.ptr == nullptr || p->k.ptr == nullptr) return FAWS_EINVAL;
   if (p->backend < FAWS_BACKEND_AUTO || p->backend > FAWS_BACKEND_TCGEN05) return FAWS_EINVAL;
   return FAWS_OK;
+}
+
+DropoutParams make_drop(const faws_problem* p) {
+  DropoutParams d{};
+  if (p->dropout_p > 0.f) {
+    d.p = p->dropout_p;
+    d.out_scale = p->dropout_scale;
+    d.seed_lo = static_cast<uint32_t>(p->philox_seed);
+    d.seed_hi = static_cast<uint32_t>(p->philox_seed >> 32);
+    d.offset = static_cast<uint32_t>(p->philox_offset);
+  }
+  return d;
 }
 
 FwdParams make_fwd(const faws_problem* p) {
@@ -45,6 +59,7 @@ FwdParams make_fwd(const faws_problem* p) {
   f.schedule = kForward;
   f.masked_bits = 0xff800000u;
   f.scores_f32 = 1;
+  f.drop = make_drop(p);
   return f;
 }
 
@@ -186,7 +201,8 @@ SoftmaxWs carve_softmax_ws(const faws_problem* p, void* ws, int n_end, int split
 // Softmax-normalised column-type sums: forward pass (out, L[, score scratch]) then the
 // key-major pass and, unless per-q-head output was asked for, the group sum.
 int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws, size_t ws_bytes,
-                     void* stream, int i_begin, int n_end, int buffered_split, int schedule) {
+                     void* stream, int i_begin, int n_end, int buffered_split, int schedule,
+                     bool dropout_in_sum = false) {
   int st = validate(p);
   if (st != FAWS_OK) return st;
   if (sum_out == nullptr) return FAWS_EINVAL;
@@ -203,6 +219,7 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   if (st != FAWS_OK) return st;
   ColSoftmaxParams c = make_cs(p, f.L, sum_out, i_begin, n_end);
   if (w.scratch != nullptr) { c.s_scratch = w.scratch; c.split = buffered_split; }
+  if (dropout_in_sum) c.drop = make_drop(p);
   if (i_begin >= p->m_end) {
     // no query of the window lies beyond the split: the sums are zero
     if (cudaMemsetAsync(sum_out, 0, (size_t)p->B * (per_q_head ? p->Hq : p->Hk) * (size_t)n_end * 4, s) != cudaSuccess)
@@ -267,8 +284,9 @@ int faws_attention_with_col_sum_sequential(const faws_problem* p, float* col_sum
 int faws_attention_with_softmax_col_sum(const faws_problem* p, float* col_sum, int32_t per_q_head,
                                         void* workspace, size_t workspace_bytes, void* stream) {
   if (p == nullptr) return FAWS_EINVAL;
+  // the one operator whose sum sees the dropout mask (attention_with_col_softmax_sum.py:238-244)
   return softmax_col_sums(p, col_sum, per_q_head, workspace, workspace_bytes, stream, 0, p->N, 0,
-                          kRoundRobin);
+                          kRoundRobin, /*dropout_in_sum=*/true);
 }
 
 int faws_attention_cross_token_qk_sum(const faws_problem* p, int32_t split, float* sum_out,

@@ -195,8 +195,12 @@ __global__ void __launch_bounds__(NT) generic_fwd_kernel(FwdParams p, int vec) {
         const bool hid = (s == FAWS_NEG_INF);
         const float pr = hid ? 0.f : exp2f((s - m_new) * kLog2e);
         rsum += hid ? 0.f : s;
-        psum += pr;
-        Ss[row * SLD + qd + 4 * c] = to_f(from_f<T>(pr));
+        psum += pr;  // the normaliser is taken before dropout (flash.py:459-460)
+        bool keep = true;
+        if (p.drop.p > 0.f)
+          keep = dropout_keep(p.drop, ((uint32_t)bh * (uint32_t)p.M + (uint32_t)(m0 + row)) * (uint32_t)p.N +
+                                          (uint32_t)(n0 + qd + 4 * c));
+        Ss[row * SLD + qd + 4 * c] = keep ? to_f(from_f<T>(pr)) : 0.f;
       }
       psum += __shfl_xor_sync(0xffffffffu, psum, 1);
       psum += __shfl_xor_sync(0xffffffffu, psum, 2);
@@ -238,9 +242,10 @@ __global__ void __launch_bounds__(NT) generic_fwd_kernel(FwdParams p, int vec) {
     if (i >= p.m_begin && i < p.m_end) {
       const float l = l_s[ty * 4 + r];
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float oscale = p.drop.p > 0.f ? p.drop.out_scale : 1.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c)
-        if (c < ncd) op[(int64_t)i * p.o_ss + tx + 16 * c] = from_f<T>(o[r][c] * inv);
+        if (c < ncd) op[(int64_t)i * p.o_ss + tx + 16 * c] = from_f<T>(o[r][c] * inv * oscale);
     }
   }
   if (p.L != nullptr && tid < BM) {
@@ -324,7 +329,10 @@ __global__ void __launch_bounds__(NT) generic_colsoftmax_kernel(ColSoftmaxParams
                   ? p.s_scratch[(bh * (p.M - p.split) + (i - p.split)) * (int64_t)p.split + j]
                   : acc[r][c] * p.sm_scale;
         }
-        Ss[(ty * 4 + r) * SLD + tx + 16 * c] = vis ? exp2f((s - Li) * kLog2e) : 0.f;
+        bool keep = vis;
+        if (vis && p.drop.p > 0.f)
+          keep = dropout_keep(p.drop, ((uint32_t)bh * (uint32_t)p.M + (uint32_t)i) * (uint32_t)p.N + (uint32_t)j);
+        Ss[(ty * 4 + r) * SLD + tx + 16 * c] = keep ? exp2f((s - Li) * kLog2e) : 0.f;
       }
     }
     __syncthreads();

@@ -14,6 +14,40 @@ namespace faws {
 enum Schedule : int { kForward = 0, kReverse = 1, kRoundRobin = 2 };
 
 // Everything a forward kernel needs.  Plain data, passed by value.
+// Dropout on the weights that multiply V.  keep(b,h,i,j) = philox6(seed, offset + linear index) > p.
+struct DropoutParams {
+  float p;            // 0 = off
+  float out_scale;    // multiplies out when p > 0
+  uint32_t seed_lo, seed_hi;
+  uint32_t offset;
+};
+
+#ifdef __CUDACC__
+// First output of Philox-4x32 with six rounds for counter (c, 0, 0, 0) and key (seed_lo, seed_hi),
+// mapped to [0, 1) the way triton's tl.rand does (sign-folded int32 times 2^-31 rounded to fp32):
+// the generator the reference kernels draw dropout masks from (flash.py:465).
+__device__ __forceinline__ float philox6_uniform(uint32_t c, uint32_t k0, uint32_t k1) {
+  uint32_t c0 = c, c1 = 0u, c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int r = 0; r < 6; ++r) {
+    const uint32_t hb = __umulhi(0xCD9E8D57u, c2), lb = 0xCD9E8D57u * c2;
+    const uint32_t ha = __umulhi(0xD2511F53u, c0), la = 0xD2511F53u * c0;
+    c0 = hb ^ c1 ^ k0;
+    c2 = ha ^ c3 ^ k1;
+    c1 = lb;
+    c3 = la;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  int x = static_cast<int>(c0);
+  x = x < 0 ? ~x : x;
+  return __int2float_rn(x) * 4.6566127342e-10f;
+}
+__device__ __forceinline__ bool dropout_keep(const DropoutParams& d, uint32_t linear_index) {
+  return philox6_uniform(d.offset + linear_index, d.seed_lo, d.seed_hi) > d.p;
+}
+#endif
+
 struct FwdParams {
   const void* q;
   const void* k;
@@ -47,6 +81,7 @@ struct FwdParams {
   int fill_ctas;         // set by the tcgen05 launcher: masked score tiles are written by extra CTAs
   int col_lin;           // column hook skips tiles that col_tile_linear() accepts (see below)
   int col_row_lo;        // max(col_row_begin, m_begin): first query row that contributes
+  DropoutParams drop;
 };
 
 // Raw column sums are linear in q: for a 128 x 128 (query tile, key tile) pair in which every
@@ -77,6 +112,7 @@ struct ColSoftmaxParams {
   int n_end;             // keys j < n_end
   const float* s_scratch;  // if non-null read scaled scores (B,Hq,M-split,split) instead of q.k
   int split;
+  DropoutParams drop;    // p > 0: dropped weights are left out of the sum (no rescale)
 };
 
 struct ReducePartialParams {

@@ -1348,6 +1348,7 @@ cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
 bool tc_fwd_supported(const FwdParams& p, int dtype) {
   (void)dtype;
   if (p.D != 64 && p.D != 128) return false;
+  if (p.drop.p > 0.f) return false;       // dropout masks are drawn by the CUDA-core kernels only
   if (!(p.sm_scale > 0.f)) return false;  // the row max is taken on unscaled scores
   if (!device_is_sm100() || get_encode() == nullptr) return false;
   if (p.m_begin % BM != 0 || p.m_end <= p.m_begin) return false;
@@ -1425,6 +1426,7 @@ bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype) {
   (void)dtype;
   if (p.D != 64 && p.D != 128) return false;
   if (p.s_scratch != nullptr) return false;  // the buffered pass reads stored scores, no MMA
+  if (p.drop.p > 0.f) return false;
   if (p.m_begin % BM != 0 || !(p.sm_scale > 0.f)) return false;
   if (!device_is_sm100() || get_encode() == nullptr) return false;
   if (!ok16(p.q, p.q_sb, p.q_sh, p.q_ss) || !ok16(p.k, p.k_sb, p.k_sh, p.k_ss)) return false;

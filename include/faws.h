@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define FAWS_VERSION 1
+#define FAWS_VERSION 2
 
 /* element types of q, k, v, out */
 #define FAWS_FP16 0
@@ -96,7 +96,20 @@ typedef struct faws_problem {
                           /* the scaled scores, -inf for empty rows           */
                           /* (flash.py:480-486)                               */
   int32_t backend;        /* FAWS_BACKEND_* */
+  /* Dropout on the softmax weights that multiply V (flash.py:463-466).  0 = off.  An entry
+   * (b,h,i,j) is kept iff u > dropout_p, u being the first output of Philox-4x32 with 6 rounds
+   * (triton's tl.rand(seed, c, n_rounds=6)) for key = philox_seed and counter
+   * c = philox_offset + ((b*Hq + h)*M + i)*N + j in 32-bit wrap-around arithmetic
+   * (flash.py:376-380).  The softmax normaliser and every raw-score output ignore the mask. */
+  float dropout_p;        /* in [0, 1) */
+  float dropout_scale;    /* out is multiplied by this when dropout_p > 0: 1/(1-p) in          */
+                          /* attention and attention_with_scores (flash.py:488-491,             */
+                          /* attention_with_scores.py:201-203), 1 in the reference's other      */
+                          /* operators, which mask without rescaling                            */
   int32_t reserved;
+  uint64_t philox_seed;
+  uint64_t philox_offset; /* < 2^31 (beyond that triton switches to its 64-bit generator:      */
+                          /* FAWS_EUNSUPPORTED)                                                 */
 } faws_problem;
 
 /* Replaces attention() forward (flash.py:264-295, kernel flash.py:335-498). */

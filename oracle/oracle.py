@@ -173,6 +173,63 @@ def linear_row_sum(q, k, causal, sm_scale=None, p_seq=0):
         ks = k.sum(dim=2, keepdim=True).expand(B, Hq, M, D)
     return (q * ks).sum(-1) * sm_scale
 
+# -- dropout (dropout_p > 0) ---------------------------------------------------
+# The reference kernels draw one uniform per (b, h, i, j) from Triton's Philox-4x32 with six
+# rounds, `tl.rand(seed, offs, n_rounds=6)` (flash.py:465), at the linear offset
+# offset + ((b*Hq + h)*M + i)*N + j computed in 32-bit arithmetic (flash.py:376-380), and keep an
+# entry iff the uniform is > dropout_p.  The generator lives in the triton package (3.6.0:
+# triton/language/random.py, `philox_impl`, `randint4x`, `uint_to_uniform_float`); it is restated
+# below from its published definition and pinned by tests/golden/dropout_philox_stream.npz, which
+# holds tl.rand outputs produced with that package.  Only the first of the four Philox outputs
+# is used; the counter is (c0, 0, 0, 0) and the key is the 64-bit seed's two halves.
+
+def philox_uniform(seed: int, offsets, n_rounds: int = 6):
+    """tl.rand(seed, offsets, n_rounds) for 32-bit offsets; returns float32 numpy array."""
+    import numpy as np
+
+    ka, kb = 0x9E3779B9, 0xBB67AE85
+    ra, rb = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+    c0 = np.asarray(offsets).astype(np.uint32)
+    c1 = np.zeros_like(c0)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    for _ in range(n_rounds):
+        pb = rb * c2.astype(np.uint64)
+        pa = ra * c0.astype(np.uint64)
+        c0, c2, c1, c3 = ((pb >> np.uint64(32)).astype(np.uint32) ^ c1 ^ np.uint32(k0),
+                          (pa >> np.uint64(32)).astype(np.uint32) ^ c3 ^ np.uint32(k1),
+                          pb.astype(np.uint32), pa.astype(np.uint32))
+        k0, k1 = (k0 + ka) & 0xFFFFFFFF, (k1 + kb) & 0xFFFFFFFF
+    x = c0.view(np.int32)
+    x = np.where(x < 0, -x - 1, x).astype(np.int32)
+    return x.astype(np.float32) * np.float32(4.6566127342e-10)
+
+
+def dropout_keep_mask(seed: int, offset: int, B: int, Hq: int, M: int, N: int, dropout_p: float):
+    """(B,Hq,M,N) bool: entries the reference kernels keep (flash.py:376-380,463-466)."""
+    import numpy as np
+
+    assert 0 <= offset < 2 ** 31, "the 64-bit Philox variant Triton switches to is not restated"
+    idx = (np.arange(B * Hq * M * N, dtype=np.uint64) + np.uint64(offset)).astype(np.uint32)
+    u = philox_uniform(seed, idx)
+    return torch.from_numpy(u > np.float32(dropout_p)).reshape(B, Hq, M, N)
+
+
+def dropout_out(scores, v, keep, dropout_p):
+    """out under dropout: (softmax(scores) * keep) @ v / (1 - p); the normaliser is taken before
+    the mask (flash.py:459-466,488-491)."""
+    Hq, Hk = scores.shape[1], v.shape[1]
+    w = softmax_weights(scores) * keep.float()
+    return torch.matmul(w, _expand_kv(v.float(), Hq // Hk)) * (1.0 / (1.0 - dropout_p))
+
+
+def dropout_softmax_col_sum(scores, keep):
+    """Softmax column sum of attention_with_softmax_col_sum under dropout: dropped weights are left
+    out and nothing is rescaled (attention_with_col_softmax_sum.py:238-244)."""
+    return (softmax_weights(scores) * keep.float()).sum(dim=-2)
+
+
 
 # ---------------------------------------------------------------------------
 # Tolerances (written once, used by every parity test).

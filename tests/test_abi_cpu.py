@@ -25,14 +25,16 @@ def test_header_symbols_exported(lib):
     assert declared == set(_lib.EXPORTS), declared ^ set(_lib.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.faws_version() == 1
+    assert lib.faws_version() == 2
 
 
 def test_struct_layout_matches_header(lib):
     from flash_attn_with_score_b200 import _lib
-    # 6+2 int32, float, 2 int32 = 44 bytes -> padded to 48; 4 tensors of 32; pointer; 2 int32
+    # 6+2 int32, float, 2 int32 = 44 bytes -> padded to 48; 4 tensors of 32; pointer;
+    # backend, dropout_p, dropout_scale, reserved; philox seed and offset
     assert C.sizeof(_lib.Tensor) == 32
-    assert C.sizeof(_lib.Problem) == 48 + 4 * 32 + 8 + 8
+    assert C.sizeof(_lib.Problem) == 48 + 4 * 32 + 8 + 16 + 16
+    assert _lib.Problem.philox_seed.offset == 48 + 4 * 32 + 8 + 16
 
 
 def test_validation_without_gpu(lib):
@@ -48,6 +50,13 @@ def test_validation_without_gpu(lib):
     p.m_end = 9
     assert lib.faws_attention(C.byref(p), None) == -1  # window
     assert lib.faws_workspace_bytes(3, C.byref(p), 0) == 0
+    p.m_end = 8
+    p.dropout_p = 1.0
+    assert lib.faws_attention(C.byref(p), None) == -1  # dropout_p outside [0, 1)
+    p.dropout_p = 0.5
+    p.philox_offset = 2 ** 31
+    assert lib.faws_attention(C.byref(p), None) == -2  # 64-bit Philox variant
+    p.dropout_p = 0.0
     assert b"workspace" in lib.faws_strerror(-3)
     assert lib.faws_reduce_ranks(None, 2, 4, None, None) == -1
 
@@ -66,8 +75,6 @@ def test_python_asserts_mirror_reference():
         F.attention_cross_token_softmax_sum(q, k, k, 9)
     with pytest.raises(AssertionError):
         F.attention(torch.zeros(1, 4, 8, 48, dtype=torch.float16), k, k)
-    with pytest.raises(NotImplementedError):
-        F.attention(q, k, k, dropout_p=0.1)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         F.attention(q, k, k)
     assert set(F.__all__) >= {
