@@ -159,10 +159,10 @@ int raw_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws
   f.col_lin = 1;  // cleared by run_fwd when the CUDA-core kernels run
   f.col_row_lo = row_begin > p->m_begin ? row_begin : p->m_begin;
   float* qsum = reinterpret_cast<float*>(static_cast<char*>(ws) + part_bytes);
+  f.qsum = qsum;  // the tcgen05 forward kernel writes the per-tile query sums itself
   int bm = 0, bn = 0;
   st = run_fwd(p, f, s, &bm, &bn);
   if (st != FAWS_OK) return st;
-  if (f.col_lin && launch_qtile_sums(f, p->dtype, qsum, s) != cudaSuccess) return FAWS_ECUDA;
   ReducePartialParams r{};
   r.partial = f.col_partial; r.out = sum_out;
   r.B = p->B; r.Hq = p->Hq; r.Hk = p->Hk; r.G = p->Hq / p->Hk; r.per_q_head = per_q_head ? 1 : 0;

@@ -422,27 +422,6 @@ __global__ void reduce_partials_kernel(ReducePartialParams p) {
   p.out[((int64_t)b * Hout + ho) * p.n_end + j] = sum;
 }
 
-// qsum[b,h,qb,d] = sum over the rows of query tile qb (128 rows from row 0) of q[b,h,row,d]
-template <typename T>
-__global__ void __launch_bounds__(128) qtile_sum_kernel(const T* q, int64_t sb, int64_t sh, int64_t ss, float* qsum,
-                                                        int Hq, int M, int D, int nqb_total) {
-  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  if (d < D) {
-    const T* base = q + b * sb + h * sh + d;
-    const int r0 = qb * 128, r1 = min(r0 + 128, M);
-    int r = r0;
-    for (; r + 3 < r1; r += 4) {
-      s0 += to_f(base[(int64_t)r * ss]);
-      s1 += to_f(base[(int64_t)(r + 1) * ss]);
-      s2 += to_f(base[(int64_t)(r + 2) * ss]);
-      s3 += to_f(base[(int64_t)(r + 3) * ss]);
-    }
-    for (; r < r1; ++r) s0 += to_f(base[(int64_t)r * ss]);
-  }
-  qsum[(((int64_t)b * Hq + h) * nqb_total + qb) * 128 + d] = (s0 + s1) + (s2 + s3);
-}
-
 // Column sums with the linear part: a block owns one 128-wide key tile t of one output head.
 // out[j] = sm_scale * sum_h k_j . V_h(t) + sum_h sum_{qb hooked} partial[h][qb][j], where
 // V_h(t) = sum of qsum[h][qb] over the query tiles for which col_tile_linear(qb, t) holds.
@@ -618,19 +597,6 @@ cudaError_t launch_reduce_partials(const ReducePartialParams& p, int dtype, cuda
     dim3 grid((p.n_end + 255) / 256, p.per_q_head ? p.Hq : p.Hk, p.B);
     reduce_partials_kernel<<<grid, 256, 0, s>>>(p);
   }
-  count_launch();
-  return cudaGetLastError();
-}
-
-cudaError_t launch_qtile_sums(const FwdParams& p, int dtype, float* qsum, cudaStream_t s) {
-  const int nqb_total = (p.M + 127) / 128;
-  dim3 grid(nqb_total, p.Hq, p.B);
-  if (dtype == FAWS_FP16)
-    qtile_sum_kernel<__half><<<grid, 128, 0, s>>>(reinterpret_cast<const __half*>(p.q), p.q_sb, p.q_sh, p.q_ss, qsum,
-                                                  p.Hq, p.M, p.D, nqb_total);
-  else
-    qtile_sum_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(p.q), p.q_sb, p.q_sh,
-                                                         p.q_ss, qsum, p.Hq, p.M, p.D, nqb_total);
   count_launch();
   return cudaGetLastError();
 }

@@ -81,6 +81,7 @@ struct FwdParams {
   int fill_ctas;         // set by the tcgen05 launcher: masked score tiles are written by extra CTAs
   int col_lin;           // column hook skips tiles that col_tile_linear() accepts (see below)
   int col_row_lo;        // max(col_row_begin, m_begin): first query row that contributes
+  float* qsum;           // col_lin: (B,Hq,ceil(M/128),128) per-tile sums of the query rows, written by the
   DropoutParams drop;
 };
 
@@ -136,7 +137,6 @@ cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cudaStream_t s);
 cudaError_t launch_reduce_partials(const ReducePartialParams& p, int dtype, cudaStream_t s);
-cudaError_t launch_qtile_sums(const FwdParams& p, int dtype, float* qsum, cudaStream_t s);
 cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, int len,
                              cudaStream_t s);
 cudaError_t launch_reduce_ranks(const float* parts, int n_ranks, int64_t count, float* out,

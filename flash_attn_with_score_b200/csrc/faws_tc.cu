@@ -107,10 +107,18 @@ struct Bars {
   uint64_t col_ready[2];  // per query tile: column-sum partial rows of its 4 warps are in smem
   uint64_t o_done;        // every MMA of the CTA has completed
   uint64_t merge_ready;   // SPLIT: warpgroup 1 has published its (m, l, row sum)
+  uint64_t qsum_done;     // column hook: warps 2-3 have finished reading the Q tiles
   uint32_t tmem_base;
   int abort_flag;
 };
 
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t w);
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t w) {
+  return __half22float2(*reinterpret_cast<__half2*>(&w));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t w) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
+}
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
@@ -273,6 +281,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     }
     mbar_init(&bars->o_done, 1);
     mbar_init(&bars->merge_ready, 128);
+    mbar_init(&bars->qsum_done, 64);
     bars->abort_flag = 0;
     mbar_fence_init();
     // This thread is also the TMA producer: start the first loads now so that their HBM
@@ -303,6 +312,37 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const int s = idx % KV_SLOTS, u = idx / KV_SLOTS;
         if (!mbar_wait(&bars->kv_empty[s], (u & 1) ^ 1, abort_flag)) break;
         issue_kv_load(idx);
+      }
+    } else if (HOOK == kHookColPart && warp >= 2) {
+      // ---------------------------------------------------------- per-tile sums of the query rows
+      // The linear part of the raw column sums needs sum_i q_i of every fully contributing query
+      // tile; the tiles are in shared memory anyway, so the two otherwise idle warps add them up.
+      // A warp reads one 128-byte swizzled row segment per step (conflict-free).
+      if (p.col_lin != 0 && p.qsum != nullptr && nt > 0) {
+        if (mbar_wait(&bars->q_full, 0, abort_flag)) {
+          const int nqb_total = (p.M + 127) / 128;
+          for (int unit = (warp - 2) * 32 + lane; unit < L::kQTiles * (D / 2); unit += 64) {
+            const int t = unit / (D / 2), pair = unit % (D / 2);
+            const int c = pair >> 5, word = pair & 31;
+            const unsigned char* base = smem + L::q_off + t * L::kTile + c * L::kSub + ((word & 3) << 2);
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll 8
+            for (int r = 0; r < BM; r += 2) {
+              const float2 x = unpack2<T>(*reinterpret_cast<const uint32_t*>(
+                  base + r * 128 + (((word >> 2) ^ (r & 7)) << 4)));
+              const float2 y = unpack2<T>(*reinterpret_cast<const uint32_t*>(
+                  base + (r + 1) * 128 + (((word >> 2) ^ ((r + 1) & 7)) << 4)));
+              a0 += x.x; a1 += x.y;
+              b0 += y.x; b1 += y.y;
+            }
+            const int r0 = m0 + t * BM;
+            if (r0 < p.M) {
+              float* dst = p.qsum + (((int64_t)bh * nqb_total + r0 / BM) * 128 + c * 64 + word * 2);
+              *reinterpret_cast<float2*>(dst) = make_float2(a0 + b0, a1 + b1);
+            }
+          }
+        }
+        mbar_arrive(&bars->qsum_done);
       }
     } else if (warp == 1 && nt > 0) {
       // ---------------------------------------------------------- MMA issuer
@@ -847,6 +887,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         // Every MMA of the CTA has completed, so the Q tiles' shared memory is free: each warp
         // stages its 32 x D output block there (128B-swizzled) and stores it with TMA.
         unsigned char* ost = smem + L::q_off + (warp - 4) * (32 * D * 2);
+        if constexpr (HOOK == kHookColPart) {  // ... once warps 2-3 have summed the Q rows
+          if (p.col_lin != 0 && p.qsum != nullptr) mbar_wait(&bars->qsum_done, 0, abort_flag);
+        }
         const float f0 = w0 * inv, f1 = w1 * inv;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
