@@ -974,9 +974,20 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 //   out[j] = sum over heads of the CTA and queries i of exp(s_ij - L_i).
 // One CTA owns 128 keys of one (batch, kv head or query head) and walks the query tiles of its
 // heads.  S^T = K.Q^T puts keys on TMEM lanes, so thread j accumulates column j in a register:
-// no cross-thread reduction, fixed order, one store.  Four S^T buffers; the two consumer
-// warpgroups take alternate query tiles and are added in a fixed order at the end.
+// no cross-thread reduction, fixed order, one store.  The pass is bound by the exponential
+// (MUFU) pipe, which a warp keeps busy only between its waits and TMEM loads, so the kernel runs
+// four consumer warpgroups (16 warps, 4 per scheduler): warpgroup w owns S^T buffer w and Q slot
+// w, takes every fourth query tile in two 64-column halves (64 live score registers), and the
+// four partial sums are added in a fixed order at the end.
 constexpr int CS_QSLOTS = 4;
+constexpr int CS_WGS = 4;
+constexpr int CS_THREADS = 128 + CS_WGS * 128;
+constexpr int CS_REGS_LAUNCH = 96;   // 65536 / 640 rounded down to the allocation unit
+constexpr int CS_REGS_AUX = 56;
+constexpr int CS_REGS_CONSUMER = 104;
+static_assert(128 * CS_REGS_AUX + CS_WGS * 128 * CS_REGS_CONSUMER <= CS_REGS_LAUNCH * CS_THREADS,
+              "setmaxnreg would block");
+static_assert(CS_QSLOTS == CS_WGS, "a warpgroup owns the slot and buffer of its index");
 
 template <int D>
 struct CsSmem {
@@ -984,9 +995,9 @@ struct CsSmem {
   static constexpr int kSub = 128 * 128;
   static constexpr int k_off = 0;
   static constexpr int q_off = k_off + kTile;
-  static constexpr int l_off = q_off + CS_QSLOTS * kTile;  // [4][128] floats: -L_i*log2e per query
-  static constexpr int comb_off = l_off + 4 * 128 * 4;     // [128] floats
-  static constexpr int bar_off = comb_off + 128 * 4;
+  static constexpr int l_off = q_off + CS_QSLOTS * kTile;  // [warpgroup][2][128] floats: -L_i*log2e per query
+  static constexpr int comb_off = l_off + CS_WGS * 2 * 128 * 4;  // [warpgroup 1..][128] floats
+  static constexpr int bar_off = comb_off + (CS_WGS - 1) * 128 * 4;
   static constexpr int total = bar_off + 256;
   static constexpr int alloc = total + 1024;
 };
@@ -995,7 +1006,7 @@ struct CsBars {
   uint64_t k_full;
   uint64_t q_full[CS_QSLOTS], q_empty[CS_QSLOTS];
   uint64_t s_full[4], s_free[4];
-  uint64_t l_ready[2];
+  uint64_t l_ready[CS_WGS];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -1005,7 +1016,7 @@ struct CsMaps {
 };
 
 template <typename T, int D>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(CS_THREADS, 1)
 tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams p, int heads_per_cta,
                      int* __restrict__ status) {
   using L = CsSmem<D>;
@@ -1043,8 +1054,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->s_free[s], 128);
     }
-    mbar_init(&bars->l_ready[0], 128);
-    mbar_init(&bars->l_ready[1], 128);
+    for (int w = 0; w < CS_WGS; ++w) mbar_init(&bars->l_ready[w], 128);
     bars->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&maps.q);
@@ -1061,7 +1071,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 
   float acc = 0.f;
   if (warp < 4) {
-    reg_dealloc<REGS_AUX>();
+    reg_dealloc<CS_REGS_AUX>();
     if (warp == 0 && lane == 0 && total > 0) {
       // ---------------------------------------------------------- TMA producer
       mbar_arrive_expect_tx(&bars->k_full, L::kTile);
@@ -1105,13 +1115,13 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       }
     }
   } else {
-    reg_alloc<REGS_SOFTMAX>();
+    reg_alloc<CS_REGS_CONSUMER>();
     // ------------------------------------------------------------ consumers: thread = key
     const int wg = (warp - 4) >> 2;
     const int lg = warp & 3;
     const int row = lg * 32 + lane;
     const int j = n0 + row;
-    const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
+    const uint32_t t_buf = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(wg * BM);
     const float scale_log2 = p.sm_scale * kLog2e;
 
     // -L_i*log2e of query tile u (for this thread's column x = row), -inf where the query is
@@ -1130,16 +1140,17 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
     bool alive = true;
     int mine = 0;  // tiles this warpgroup has processed
 #ifdef FAWS_TRACE
-    long long cs_wait_l = 0, cs_wait_s = 0, cs_ld = 0, cs_comp = 0, cs_pre = 0; int cs_tiles = 0;
+    long long cs_wait_l = 0, cs_wait_s = 0, cs_ld = 0, cs_comp = 0; int cs_tiles = 0;
     const long long cs_t0 = clock64();
 #endif
     float negl_next = (wg < total) ? load_negl(wg) : FAWS_NEG_INF;
-    for (int u = wg; u < total; u += 2, ++mine) {
-      const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
-      float* lb = lbuf + s * 128;
-      lb[row] = negl_next;  // slot s was last read by this warpgroup two tiles ago (before its l_ready wait)
+    for (int u = wg; u < total; u += CS_WGS, ++mine) {
+      // Two L buffers per warpgroup: the barrier below completes only when every thread of the
+      // warpgroup has finished the previous tile, so the buffer of the tile before that is free.
+      float* lb = lbuf + (wg * 2 + (mine & 1)) * 128;
+      lb[row] = negl_next;
       mbar_arrive(&bars->l_ready[wg]);
-      if (u + 2 < total) negl_next = load_negl(u + 2);
+      if (u + CS_WGS < total) negl_next = load_negl(u + CS_WGS);
 #ifdef FAWS_TRACE
       const long long cw0 = clock64();
 #endif
@@ -1147,81 +1158,89 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 #ifdef FAWS_TRACE
       const long long cw1 = clock64();
 #endif
-      if (!mbar_wait(&bars->s_full[s], use & 1, abort_flag)) { alive = false; break; }
+      if (!mbar_wait(&bars->s_full[wg], mine & 1, abort_flag)) { alive = false; break; }
 #ifdef FAWS_TRACE
       const long long cw2 = clock64();
       cs_wait_l += cw1 - cw0; cs_wait_s += cw2 - cw1; ++cs_tiles;
 #endif
       tc_fence_after();
-      uint32_t r[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        tmem_ld32(t_lane + (uint32_t)(s * BM) + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bars->s_free[s]);
-#ifdef FAWS_TRACE
-      const long long cw3 = clock64();
-      cs_ld += cw3 - cw2;
-#endif
-
       const int g = u / ntq, qt = qt0 + (u - g * ntq);
       const int i0 = qt * BM;
       // causal: query column x is visible to key j iff i0 + x + p_seq >= j
       const int xlo = p.causal ? (j - p.p_seq - i0) : 0;
       const bool full = !p.causal || (n0 + BN - 1 - p.p_seq - i0 <= 0);
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      if (full) {
-#if FAWS_F32X2
-        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
-        uint64_t ap0 = 0ull, ap1 = 0ull;
-#pragma unroll
-        for (int x = 0; x < 128; x += 4) {
-          const float4 nl = *reinterpret_cast<const float4*>(lb + x);
-          float t0, t1, t2, t3;
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2,
-                                 pack_f32x2(nl.x, nl.y)), t0, t1);
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3])), scale2,
-                                 pack_f32x2(nl.z, nl.w)), t2, t3);
-          ap0 = add_f32x2(ap0, pack_f32x2(fast_exp2(t0), fast_exp2(t1)));
-          ap1 = add_f32x2(ap1, pack_f32x2(fast_exp2(t2), fast_exp2(t3)));
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+#ifdef FAWS_TRACE
+        const long long ch0 = clock64();
+#endif
+        uint32_t r[64];
+        tmem_ld32(t_buf + half * 64, reinterpret_cast<uint32_t(&)[32]>(r[0]));
+        tmem_ld32(t_buf + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
+        tmem_wait_ld();
+        if (half == 1) {  // the buffer can take the next S^T of this warpgroup
+          tc_fence_before();
+          mbar_arrive(&bars->s_free[wg]);
         }
-        unpack_f32x2(ap0, a0, a1);
-        unpack_f32x2(ap1, a2, a3);
+#ifdef FAWS_TRACE
+        const long long ch1 = clock64();
+        cs_ld += ch1 - ch0;
+#endif
+        const float* lh = lb + half * 64;
+        if (full) {
+#if FAWS_F32X2
+          const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+          uint64_t ap0 = pack_f32x2(a0, a1), ap1 = pack_f32x2(a2, a3);
+#pragma unroll
+          for (int x = 0; x < 64; x += 4) {
+            const float4 nl = *reinterpret_cast<const float4*>(lh + x);
+            float t0, t1, t2, t3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2,
+                                   pack_f32x2(nl.x, nl.y)), t0, t1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3])), scale2,
+                                   pack_f32x2(nl.z, nl.w)), t2, t3);
+            ap0 = add_f32x2(ap0, pack_f32x2(fast_exp2(t0), fast_exp2(t1)));
+            ap1 = add_f32x2(ap1, pack_f32x2(fast_exp2(t2), fast_exp2(t3)));
+          }
+          unpack_f32x2(ap0, a0, a1);
+          unpack_f32x2(ap1, a2, a3);
 #else
 #pragma unroll
-        for (int x = 0; x < 128; x += 4) {
-          const float4 nl = *reinterpret_cast<const float4*>(lb + x);
-          a0 += fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x));
-          a1 += fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y));
-          a2 += fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z));
-          a3 += fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w));
-        }
+          for (int x = 0; x < 64; x += 4) {
+            const float4 nl = *reinterpret_cast<const float4*>(lh + x);
+            a0 += fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x));
+            a1 += fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y));
+            a2 += fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z));
+            a3 += fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w));
+          }
 #endif
-      } else {
+        } else {
+          const int xh = xlo - half * 64;
 #pragma unroll
-        for (int x = 0; x < 128; x += 4) {
-          const float4 nl = *reinterpret_cast<const float4*>(lb + x);
-          a0 += (x >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x)) : 0.f;
-          a1 += (x + 1 >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y)) : 0.f;
-          a2 += (x + 2 >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z)) : 0.f;
-          a3 += (x + 3 >= xlo) ? fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w)) : 0.f;
+          for (int x = 0; x < 64; x += 4) {
+            const float4 nl = *reinterpret_cast<const float4*>(lh + x);
+            a0 += (x >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x)) : 0.f;
+            a1 += (x + 1 >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y)) : 0.f;
+            a2 += (x + 2 >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z)) : 0.f;
+            a3 += (x + 3 >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w)) : 0.f;
+          }
         }
+#ifdef FAWS_TRACE
+        cs_comp += clock64() - ch1;
+#endif
       }
       acc += (a0 + a1) + (a2 + a3);
-#ifdef FAWS_TRACE
-      cs_comp += clock64() - cw3;
-#endif
     }
 #ifdef FAWS_TRACE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0 && wg < 2) {
       long long* o = g_trace + 2 * 4096 + 4020 + wg * 4;
       o[0] = cs_wait_l; o[1] = cs_wait_s; o[2] = cs_tiles; o[3] = clock64() - cs_t0;
       g_trace[2 * 4096 + 4030 + wg * 2] = cs_ld; g_trace[2 * 4096 + 4031 + wg * 2] = cs_comp;
     }
 #endif
     if (!alive) acc = 0.f;
-    if (wg == 1) comb[row] = acc;
+    if (wg > 0) comb[(wg - 1) * 128 + row] = acc;
   }
 
   // ------------------------------------------------------------ common exit
@@ -1230,7 +1249,8 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
   if (warp >= 4 && warp < 8) {
     const int row = (warp & 3) * 32 + lane;
     const int j = n0 + row;
-    if (j < p.n_end) p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = acc + comb[row];
+    if (j < p.n_end)  // warpgroups 0..3 in this order
+      p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = ((acc + comb[row]) + comb[128 + row]) + comb[256 + row];
   }
   if (*abort_flag) {
     if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
@@ -1489,7 +1509,7 @@ cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads
   }
   const int nkt = (p.n_end + BN - 1) / BN;
   dim3 grid = p.causal ? dim3(p.Hq / heads_per_cta, p.B, nkt) : dim3(nkt, p.Hq / heads_per_cta, p.B);
-  tc_colsoftmax_kernel<T, D><<<grid, NTHREADS, L::alloc, s>>>(maps, p, heads_per_cta, device_status_word());
+  tc_colsoftmax_kernel<T, D><<<grid, CS_THREADS, L::alloc, s>>>(maps, p, heads_per_cta, device_status_word());
   count_launch();
   return cudaGetLastError();
 }
