@@ -425,12 +425,18 @@ __global__ void reduce_partials_kernel(ReducePartialParams p) {
 // Column sums with the linear part: a block owns one 128-wide key tile t of one output head.
 // out[j] = sm_scale * sum_h k_j . V_h(t) + sum_h sum_{qb hooked} partial[h][qb][j], where
 // V_h(t) = sum of qsum[h][qb] over the query tiles for which col_tile_linear(qb, t) holds.
+// Four thread groups of 128 work on four heads of the group at a time (the per-head chains of
+// dependent global loads are what the kernel waits for); their sums are combined in the fixed
+// order group 0..3 at the end.
+constexpr int kLinGroups = 4;
+
 template <typename T>
-__global__ void __launch_bounds__(128) reduce_colsum_lin_kernel(ReducePartialParams p) {
+__global__ void __launch_bounds__(128 * kLinGroups) reduce_colsum_lin_kernel(ReducePartialParams p) {
   constexpr int LDK = 130;                 // padded row (elements): conflict-free column walks
   __shared__ T Ks[128 * LDK];              // the key tile, loaded once and reused by every head
-  __shared__ float V[128];
-  const int t = blockIdx.x, tid = threadIdx.x;
+  __shared__ float V[kLinGroups][128];
+  __shared__ float comb[kLinGroups - 1][2][128];
+  const int t = blockIdx.x, tid = threadIdx.x & 127, tg = threadIdx.x >> 7;
   const int j = t * 128 + tid;
   const int ho = blockIdx.y, b = blockIdx.z;
   const int h0 = p.per_q_head ? ho : ho * p.G;
@@ -444,7 +450,7 @@ __global__ void __launch_bounds__(128) reduce_colsum_lin_kernel(ReducePartialPar
     const int chunks = p.D >> 3;  // 16-byte chunks per row
     if (vec) {
 #pragma unroll 4
-      for (int idx = tid; idx < 128 * chunks; idx += 128) {
+      for (int idx = threadIdx.x; idx < 128 * chunks; idx += 128 * kLinGroups) {
         const int row = idx / chunks, c = idx - row * chunks;
         const int jr = t * 128 + row;
         uint4 w = make_uint4(0u, 0u, 0u, 0u);
@@ -453,7 +459,7 @@ __global__ void __launch_bounds__(128) reduce_colsum_lin_kernel(ReducePartialPar
         dst[0] = w.x; dst[1] = w.y; dst[2] = w.z; dst[3] = w.w;
       }
     } else {
-      for (int idx = tid; idx < 128 * p.D; idx += 128) {
+      for (int idx = threadIdx.x; idx < 128 * p.D; idx += 128 * kLinGroups) {
         const int row = idx / p.D, c = idx - row * p.D;
         const int jr = t * 128 + row;
         Ks[row * LDK + c] = jr < p.N ? kbase[(int64_t)jr * p.k_ss + c] : from_f<T>(0.f);
@@ -461,33 +467,40 @@ __global__ void __launch_bounds__(128) reduce_colsum_lin_kernel(ReducePartialPar
     }
   }
   float lin_sum = 0.f, part_sum = 0.f;
-  for (int g = 0; g < nh; ++g) {
-    const int h = h0 + g;
+  for (int g0 = 0; g0 < nh; g0 += kLinGroups) {  // uniform trip count: barriers inside
+    const int g = g0 + tg;
+    const bool g_ok = g < nh;
+    const int h = h0 + (g_ok ? g : 0);
     float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
-    if (tid < p.D) {
+    if (g_ok && tid < p.D) {
       const float* qs = p.qsum + (((int64_t)b * p.Hq + h) * p.nqb_total) * 128 + tid;
       int qb = 0;
-      for (; qb + 3 < p.nqb_total; qb += 4) {  // loads first, predicates after: four in flight
-        const float x0 = qs[(int64_t)qb * 128], x1 = qs[(int64_t)(qb + 1) * 128];
-        const float x2 = qs[(int64_t)(qb + 2) * 128], x3 = qs[(int64_t)(qb + 3) * 128];
-        v0 += col_tile_linear(qb, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x0 : 0.f;
-        v1 += col_tile_linear(qb + 1, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x1 : 0.f;
-        v2 += col_tile_linear(qb + 2, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x2 : 0.f;
-        v3 += col_tile_linear(qb + 3, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x3 : 0.f;
+      for (; qb + 7 < p.nqb_total; qb += 8) {  // loads first, predicates after: eight in flight
+        float x[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = qs[(int64_t)(qb + e) * 128];
+#pragma unroll
+        for (int e = 0; e < 8; e += 4) {
+          v0 += col_tile_linear(qb + e, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x[e] : 0.f;
+          v1 += col_tile_linear(qb + e + 1, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x[e + 1] : 0.f;
+          v2 += col_tile_linear(qb + e + 2, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x[e + 2] : 0.f;
+          v3 += col_tile_linear(qb + e + 3, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? x[e + 3] : 0.f;
+        }
       }
       for (; qb < p.nqb_total; ++qb)
         v0 += col_tile_linear(qb, t, p.row_lo, p.m_end, p.N, p.causal, p.p_seq) ? qs[(int64_t)qb * 128] : 0.f;
     }
-    __syncthreads();  // K tile loaded (first pass); previous head's V consumed
-    V[tid] = (v0 + v1) + (v2 + v3);
+    __syncthreads();  // K tile loaded (first pass); previous heads' V consumed
+    V[tg][tid] = (v0 + v1) + (v2 + v3);
     __syncthreads();
-    if (j_ok) {
+    if (g_ok && j_ok) {
       float d0 = 0.f, d1 = 0.f;
       const T* kr = &Ks[tid * LDK];
+      const float* Vg = V[tg];
 #pragma unroll 8
       for (int d = 0; d < p.D; d += 2) {
-        d0 = fmaf(to_f(kr[d]), V[d], d0);
-        d1 = fmaf(to_f(kr[d + 1]), V[d + 1], d1);
+        d0 = fmaf(to_f(kr[d]), Vg[d], d0);
+        d1 = fmaf(to_f(kr[d + 1]), Vg[d + 1], d1);
       }
       lin_sum += d0 + d1;
       const float* base = p.partial + ((int64_t)(b * p.Hq + h) * p.n_qb_part) * p.ncols_pad + j;
@@ -506,7 +519,19 @@ __global__ void __launch_bounds__(128) reduce_colsum_lin_kernel(ReducePartialPar
       part_sum += p0 + p1;
     }
   }
-  if (j < p.n_end) p.out[((int64_t)b * Hout + ho) * p.n_end + j] = j_ok ? (p.sm_scale * lin_sum + part_sum) : 0.f;
+  if (tg > 0) {
+    comb[tg - 1][0][tid] = lin_sum;
+    comb[tg - 1][1][tid] = part_sum;
+  }
+  __syncthreads();
+  if (tg == 0 && j < p.n_end) {
+#pragma unroll
+    for (int w = 0; w < kLinGroups - 1; ++w) {
+      lin_sum += comb[w][0][tid];
+      part_sum += comb[w][1][tid];
+    }
+    p.out[((int64_t)b * Hout + ho) * p.n_end + j] = j_ok ? (p.sm_scale * lin_sum + part_sum) : 0.f;
+  }
 }
 
 __global__ void group_sum_kernel(const float* in, float* out, int Hk, int G, int len) {
@@ -591,8 +616,8 @@ cudaError_t launch_reduce_partials(const ReducePartialParams& p, int dtype, cuda
   if (p.n_end <= 0) return cudaSuccess;
   if (p.lin) {
     dim3 grid((p.n_end + 127) / 128, p.per_q_head ? p.Hq : p.Hk, p.B);
-    if (dtype == FAWS_FP16) reduce_colsum_lin_kernel<__half><<<grid, 128, 0, s>>>(p);
-    else reduce_colsum_lin_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(p);
+    if (dtype == FAWS_FP16) reduce_colsum_lin_kernel<__half><<<grid, 128 * kLinGroups, 0, s>>>(p);
+    else reduce_colsum_lin_kernel<__nv_bfloat16><<<grid, 128 * kLinGroups, 0, s>>>(p);
   } else {
     dim3 grid((p.n_end + 255) / 256, p.per_q_head ? p.Hq : p.Hk, p.B);
     reduce_partials_kernel<<<grid, 256, 0, s>>>(p);
