@@ -976,15 +976,25 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 // heads.  S^T = K.Q^T puts keys on TMEM lanes, so thread j accumulates column j in a register:
 // no cross-thread reduction, fixed order, one store.  The pass is bound by the exponential
 // (MUFU) pipe, which a warp keeps busy only between its waits and TMEM loads, so the kernel runs
-// four consumer warpgroups (16 warps, 4 per scheduler): warpgroup w owns S^T buffer w and Q slot
-// w, takes every fourth query tile in two 64-column halves (64 live score registers), and the
-// four partial sums are added in a fixed order at the end.
-constexpr int CS_QSLOTS = 4;
-constexpr int CS_WGS = 4;
+// CS_WGS = 4 consumer warpgroups (16 warps, 4 per scheduler): warpgroup w owns S^T buffer w and Q
+// slot w, takes every fourth query tile in chunks of CS_CHUNK columns (that many live score
+// registers), and the partial sums are added in a fixed order at the end.
+#ifndef FAWS_CS_WGS
+#define FAWS_CS_WGS 4
+#endif
+#ifndef FAWS_CS_CHUNK
+#define FAWS_CS_CHUNK 64
+#endif
+#ifndef FAWS_CS_F32X2
+#define FAWS_CS_F32X2 FAWS_F32X2
+#endif
+constexpr int CS_WGS = FAWS_CS_WGS;
+constexpr int CS_QSLOTS = CS_WGS;
+constexpr int CS_CHUNK = FAWS_CS_CHUNK;  // score columns a consumer thread holds at a time
 constexpr int CS_THREADS = 128 + CS_WGS * 128;
-constexpr int CS_REGS_LAUNCH = 96;   // 65536 / 640 rounded down to the allocation unit
+constexpr int CS_REGS_LAUNCH = (65536 / CS_THREADS) & ~7;  // what the launch bound lets ptxas allocate
 constexpr int CS_REGS_AUX = 56;
-constexpr int CS_REGS_CONSUMER = 104;
+constexpr int CS_REGS_CONSUMER = ((CS_REGS_LAUNCH * CS_THREADS - 128 * CS_REGS_AUX) / (CS_WGS * 128)) & ~7;
 static_assert(128 * CS_REGS_AUX + CS_WGS * 128 * CS_REGS_CONSUMER <= CS_REGS_LAUNCH * CS_THREADS,
               "setmaxnreg would block");
 static_assert(CS_QSLOTS == CS_WGS, "a warpgroup owns the slot and buffer of its index");
@@ -1005,7 +1015,7 @@ struct CsSmem {
 struct CsBars {
   uint64_t k_full;
   uint64_t q_full[CS_QSLOTS], q_empty[CS_QSLOTS];
-  uint64_t s_full[4], s_free[4];
+  uint64_t s_full[CS_QSLOTS], s_free[CS_QSLOTS];
   uint64_t l_ready[CS_WGS];
   uint32_t tmem_base;
   int abort_flag;
@@ -1171,15 +1181,16 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       const bool full = !p.causal || (n0 + BN - 1 - p.p_seq - i0 <= 0);
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      for (int c0 = 0; c0 < BM; c0 += CS_CHUNK) {
 #ifdef FAWS_TRACE
         const long long ch0 = clock64();
 #endif
-        uint32_t r[64];
-        tmem_ld32(t_buf + half * 64, reinterpret_cast<uint32_t(&)[32]>(r[0]));
-        tmem_ld32(t_buf + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(r[32]));
+        uint32_t r[CS_CHUNK];
+#pragma unroll
+        for (int c = 0; c < CS_CHUNK; c += 32)
+          tmem_ld32(t_buf + c0 + c, reinterpret_cast<uint32_t(&)[32]>(r[c]));
         tmem_wait_ld();
-        if (half == 1) {  // the buffer can take the next S^T of this warpgroup
+        if (c0 + CS_CHUNK == BM) {  // the buffer can take the next S^T of this warpgroup
           tc_fence_before();
           mbar_arrive(&bars->s_free[wg]);
         }
@@ -1187,13 +1198,13 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
         const long long ch1 = clock64();
         cs_ld += ch1 - ch0;
 #endif
-        const float* lh = lb + half * 64;
+        const float* lh = lb + c0;
         if (full) {
-#if FAWS_F32X2
+#if FAWS_CS_F32X2
           const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
           uint64_t ap0 = pack_f32x2(a0, a1), ap1 = pack_f32x2(a2, a3);
 #pragma unroll
-          for (int x = 0; x < 64; x += 4) {
+          for (int x = 0; x < CS_CHUNK; x += 4) {
             const float4 nl = *reinterpret_cast<const float4*>(lh + x);
             float t0, t1, t2, t3;
             unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2,
@@ -1207,7 +1218,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           unpack_f32x2(ap1, a2, a3);
 #else
 #pragma unroll
-          for (int x = 0; x < 64; x += 4) {
+          for (int x = 0; x < CS_CHUNK; x += 4) {
             const float4 nl = *reinterpret_cast<const float4*>(lh + x);
             a0 += fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x));
             a1 += fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y));
@@ -1216,9 +1227,9 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           }
 #endif
         } else {
-          const int xh = xlo - half * 64;
+          const int xh = xlo - c0;
 #pragma unroll
-          for (int x = 0; x < 64; x += 4) {
+          for (int x = 0; x < CS_CHUNK; x += 4) {
             const float4 nl = *reinterpret_cast<const float4*>(lh + x);
             a0 += (x >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x)) : 0.f;
             a1 += (x + 1 >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y)) : 0.f;
@@ -1249,8 +1260,12 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
   if (warp >= 4 && warp < 8) {
     const int row = (warp & 3) * 32 + lane;
     const int j = n0 + row;
-    if (j < p.n_end)  // warpgroups 0..3 in this order
-      p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = ((acc + comb[row]) + comb[128 + row]) + comb[256 + row];
+    if (j < p.n_end) {  // warpgroups 0, 1, 2, ... in this order
+      float total_sum = acc;
+#pragma unroll
+      for (int w = 0; w < CS_WGS - 1; ++w) total_sum += comb[w * 128 + row];
+      p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = total_sum;
+    }
   }
   if (*abort_flag) {
     if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
