@@ -16,7 +16,7 @@ Deliberate differences, all keyword-only:
   * ``dropout_p > 0`` draws the same mask as the reference kernels (Philox stream of
     ``tl.rand(seed, offset + linear index, n_rounds=6)``, flash.py:376-380,463-466) with seed and
     offset taken from, and advanced on, torch's CUDA generator exactly as dropout.py:5-15 does;
-    ``philox=(seed, offset)`` pins them instead.  Dropout problems run on the CUDA-core kernels.
+    ``philox=(seed, offset)`` pins them instead.
 """
 from __future__ import annotations
 

@@ -157,7 +157,7 @@ enum Hook : int {
   kHookScores16 = 5  // scores in the input dtype (what the reference kernel writes)
 };
 
-template <typename T, int D, int HOOK, bool SPLIT>
+template <typename T, int D, int HOOK, bool SPLIT, bool DROP = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __restrict__ status) {
   using L = Smem<D, SPLIT>;
@@ -241,7 +241,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           }
         }
         tma_store_commit();
-        tma_store_wait<0>();
+        tma_store_wait_read<0>();  // the tile may go once the stores have read it; the grid ends after they land
       }
 #ifdef FAWS_TRACE
       __syncthreads();
@@ -546,6 +546,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     const int qb128 = r_tile / BM;
     const bool part_on = HOOK == kHookColPart && qb128 >= p.qb_first && r_tile < p.m_end;
     const float masked_f = __uint_as_float(p.masked_bits);
+    // Philox counter of (b, h, i, key 0) without the call's offset, 32-bit wrap-around
+    const uint32_t drop_row = ((uint32_t)bh * (uint32_t)p.M + (uint32_t)i) * (uint32_t)p.N;
 
     float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
     bool alive = true;
@@ -649,6 +651,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           l2 += e[2] + e[6];
           l3 += e[3] + e[7];
 #endif
+          if constexpr (DROP) {
+            // dropout acts on the weights that multiply V only; the row sums above are taken
+            // before it (flash.py:459-466)
+            const uint32_t base = drop_row + (uint32_t)(n0 + c * 32 + g * 8);
+#pragma unroll
+            for (int y = 0; y < 8; ++y)
+              if (!dropout_keep(p.drop, base + (uint32_t)y)) e[y] = 0.f;
+          }
           pk[g * 4 + 0] = pack2<T>(e[0], e[1]);
           pk[g * 4 + 1] = pack2<T>(e[2], e[3]);
           pk[g * 4 + 2] = pack2<T>(e[4], e[5]);
@@ -882,7 +892,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
     }
     if (write_out) {
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      if constexpr (DROP) inv *= p.drop.out_scale;
       if (my_nt > 0) {
         // Every MMA of the CTA has completed, so the Q tiles' shared memory is free: each warp
         // stages its 32 x D output block there (128B-swizzled) and stores it with TMA.
@@ -944,7 +955,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
     }
     TRACE(31);
-    if (lane < 2) tma_store_wait<0>();
+    if (lane < 2) tma_store_wait_read<0>();  // staging buffers read; completion is covered by grid completion
     TRACE(32);
     TRACE_END();
   }
@@ -1362,12 +1373,12 @@ int* device_status_word() {
   return words[dev];
 }
 
-template <typename T, int D, int HOOK, bool SPLIT>
+template <typename T, int D, int HOOK, bool SPLIT, bool DROP = false>
 cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
   using L = Smem<D, SPLIT>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<T, D, HOOK, SPLIT>,
+    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
     if (e != cudaSuccess) return e;
     attr_set = true;
@@ -1381,7 +1392,7 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   pp.fill_ctas = ((HOOK == kHookScores || HOOK == kHookScores16) && p.causal && p.p_seq + p.m_begin + 128 < p.N) ? 1 : 0;
   const int nslots = pp.fill_ctas ? 2 * ncb : ncb;
   dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, nslots) : dim3(nslots, p.Hq, p.B);
-  tc_fwd_kernel<T, D, HOOK, SPLIT><<<grid, NTHREADS, L::alloc, s>>>(maps, pp, device_status_word());
+  tc_fwd_kernel<T, D, HOOK, SPLIT, DROP><<<grid, NTHREADS, L::alloc, s>>>(maps, pp, device_status_word());
   count_launch();
   return cudaGetLastError();
 }
@@ -1405,6 +1416,10 @@ template <typename T, int D, int HOOK>
 cudaError_t launch_fwd_h(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
   // Score-materialising causal launches are bound by their stores, not by the chain of key
   // tiles: measured, the 256-row CTAs (half as many set-ups) are faster there.
+  if constexpr (HOOK != kHookScores16 && HOOK != kHookScratch) {
+    // dropout: 256-row CTAs only (the mask generation, not the chain of key tiles, bounds it)
+    if (p.drop.p > 0.f) return launch_fwd_s<T, D, HOOK, false, true>(maps, p, s);
+  }
   const bool store_bound = (HOOK == kHookScores || HOOK == kHookScores16) && p.causal;
   static const bool forced = std::getenv("FAWS_SPLIT_KV") != nullptr;
   const bool split = use_split_kv(p) && (forced || !store_bound);
@@ -1426,7 +1441,8 @@ cudaError_t launch_fwd_t(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
 bool tc_fwd_supported(const FwdParams& p, int dtype) {
   (void)dtype;
   if (p.D != 64 && p.D != 128) return false;
-  if (p.drop.p > 0.f) return false;       // dropout masks are drawn by the CUDA-core kernels only
+  if (p.drop.p > 0.f && (p.s_scratch != nullptr || (p.scores != nullptr && !p.scores_f32)))
+    return false;  // no dropout variant of the scratch and 16-bit-score hooks: CUDA-core kernels
   if (!(p.sm_scale > 0.f)) return false;  // the row max is taken on unscaled scores
   if (!device_is_sm100() || get_encode() == nullptr) return false;
   if (p.m_begin % BM != 0 || p.m_end <= p.m_begin) return false;

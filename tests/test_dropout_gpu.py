@@ -51,13 +51,15 @@ def test_matches_reference_kernels_under_dropout(path):
                 assert ok, (key, viol)
 
 
+@pytest.mark.parametrize("backend", ["generic", "auto"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
 @pytest.mark.parametrize("shape,causal,p_drop,philox", [
     ((1, 4, 2, 200, 200, 64), True, 0.2, (99, 0)),
     ((2, 2, 2, 130, 77, 128), False, 0.5, ((3 << 32) | 5, 12344)),
     ((1, 3, 1, 64, 300, 32), True, 0.05, (2 ** 63 - 1, 2 ** 31 - 5000)),  # linear index passes 2**31
-], ids=["causal_gqa", "full_ragged_d128", "offset_wraps_int32"])
-def test_matches_oracle_under_dropout(shape, causal, p_drop, philox, dtype):
+    ((1, 2, 1, 520, 392, 128), True, 0.25, (17, 2 ** 31 - 100000)),  # several tiles per row, M > N
+], ids=["causal_gqa", "full_ragged_d128", "offset_wraps_int32", "multi_tile_d128"])
+def test_matches_oracle_under_dropout(shape, causal, p_drop, philox, dtype, backend):
     B, Hq, Hk, M, N, D = shape
     g = torch.Generator().manual_seed(5)
     q = torch.randn(B, Hq, M, D, generator=g).to(dtype)
@@ -70,8 +72,9 @@ def test_matches_oracle_under_dropout(shape, causal, p_drop, philox, dtype):
     qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
     split = max(1, N // 3)
     for key, fn, rescale in OPS:
-        out, aux = fn(qd, kd, vd, causal, split, dropout_p=p_drop, philox=philox)
-        assert rescale is None or F.last_backend() == "generic"
+        out, aux = fn(qd, kd, vd, causal, split, dropout_p=p_drop, philox=philox, backend=backend)
+        if backend == "auto" and D >= 64 and rescale is not None and (key != "scores" or N % 4 == 0):
+            assert F.last_backend() == "tcgen05", key  # the mask is drawn inside the tcgen05 kernel
         if rescale is None:
             ref = orc.naive_attention_with_scores(q, k, v, causal, p_seq=N - M)[0]
         else:
@@ -110,7 +113,8 @@ def test_generator_bookkeeping_and_replay():
 
 def test_dropout_rejections():
     q = torch.randn(1, 2, 128, 64, device="cuda", dtype=torch.float16)
-    with pytest.raises(RuntimeError):  # the tcgen05 kernels draw no masks
-        F.attention(q, q, q, True, dropout_p=0.1, philox=(1, 0), backend="tcgen05")
+    with pytest.raises(RuntimeError):  # no dropout variant of the 16-bit-score hook on tcgen05
+        F.attention_with_scores(q, q, q, True, dropout_p=0.1, philox=(1, 0), backend="tcgen05",
+                                scores_dtype=torch.float16)
     with pytest.raises(NotImplementedError):
         F.attention(q, q, q, True, dropout_p=0.1, philox=(1, 2 ** 31))
