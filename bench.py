@@ -173,6 +173,11 @@ def cpu_reference_time(cfg, runs):
 def run_reference(args, rank):
     if rank != 0:
         return
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 for its workers)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
     cfg = CFG2
     flops, nbytes = algorithmic(cfg)
     score_bytes = cfg["B"] * cfg["Hq"] * cfg["S"] * cfg["S"] * 4
