@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, no multicast), tcgen05 MMA / TMEM.
+// mbarrier, TMA (cp.async.bulk.tensor, every load lands in the issuing CTA only), tcgen05 MMA / TMEM.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
