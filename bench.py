@@ -258,6 +258,42 @@ def ops_table(F, device, pk):
     return rows
 
 
+def query_split_leg(F, device, world, pk):
+    """The one path with a collective: the query rows of every head of cfg5 are split over the ranks
+    (K/V replicated), each rank runs attention_with_softmax_col_sum on its row window, the fp32
+    partial column sums are all-gathered over NCCL and added in rank order on every rank.  Strong
+    scaling (the whole cfg5 problem at every N); device time, max over ranks."""
+    import torch.distributed as dist
+    from flash_attn_with_score_b200 import shard
+    cfg = dict(B=4, Hq=32, Hk=8, S=16384, D=128, dtype=torch.bfloat16, causal=False, vdist="uniform")
+    q, k, v = make_inputs(cfg, 0, device)  # same seed on every rank: identical tensors
+    steps = 3
+    shard.query_split(F.attention_with_softmax_col_sum, q, k, v, False)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        out, sums, rows = shard.query_split(F.attention_with_softmax_col_sum, q, k, v, False)
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    digest = sums.double().sum().reshape(1)
+    lo, hi = digest.clone(), digest.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    flops, _ = algorithmic(cfg, "softmax_col_sum", None)
+    ms = t.item()
+    return {"workload": "cfg5", "op": "attention_with_softmax_col_sum", "scaling": "strong", "n_gpus": world,
+            "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps,
+            "rows_per_rank": rows[1] - rows[0],
+            "collective": "all_gather of the fp32 partial column sums + fixed-order reduce kernel",
+            "exchanged_bytes_per_rank": int(sums.numel() * 4 * (world - 1)),
+            "sums_identical_on_all_ranks": bool((lo == hi).item()),
+            "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (world * pk["tensor"])}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -411,6 +447,10 @@ def main():
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv))
     d2h = h_out.numel() * h_out.element_size() + h_scores.numel() * 4
 
+    qsplit = None
+    if world > 1 and not args.no_ops:
+        qsplit = query_split_leg(F, device, world, pk)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -435,6 +475,8 @@ def main():
         "gpu_launches": launches, "backend": F.last_backend(), "device_status": status, "clocks": clocks,
     }
     line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
+    if qsplit is not None:
+        line["query_split"] = qsplit
     if world == 1 and not args.no_cpu:
         ts = cpu_reference_time(cfg, 5)
         sec = statistics.median(ts)
