@@ -179,6 +179,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The next forward launch of the stream may place its CTAs on SMs this grid no longer needs
+  // (it waits at griddep_wait() before it touches global memory).
+  griddep_launch_dependents();
   // Launch order.  Default: row blocks fastest, so the CTAs of a head run together and share its
   // K/V through L2.  lpt_order (causal, K/V small enough to stay in L2 anyway): row blocks
   // slowest, so the heaviest row blocks of every head are dispatched first (longest-processing-
@@ -228,6 +231,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(tile + lane * 128 + (cc << 4)) = fill;
       fence_proxy_async_smem();
+      griddep_wait();  // the previous kernel of the stream may still be reading or writing the scores
       __syncwarp();
       if (lane == 0) {
         constexpr int kGroups = CTA_ROWS / 32;
@@ -294,7 +298,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     bars->abort_flag = 0;
     mbar_fence_init();
     // This thread is also the TMA producer: start the first loads now so that their HBM
-    // latency overlaps the TMEM allocation and the set-up barrier.
+    // latency overlaps the TMEM allocation and the set-up barrier.  Everything before this
+    // point (barriers, descriptor prefetch) touched no global data and may overlap the previous
+    // kernel of the stream.
+    griddep_wait();
     if (nt > 0) {
       mbar_arrive_expect_tx(&bars->q_full, L::kQTiles * L::kTile);
       for (int t = 0; t < L::kQTiles; ++t)
@@ -308,6 +315,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     tmem_alloc(&bars->tmem_base, TMEM_COLS);
     tmem_relinquish();
   }
+  griddep_wait();  // every thread, before its first global access
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1403,9 +1411,23 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   pp.fill_ctas = ((HOOK == kHookScores || HOOK == kHookScores16) && p.causal && p.p_seq + p.m_begin + 128 < p.N) ? 1 : 0;
   const int nslots = pp.fill_ctas ? 2 * ncb : ncb;
   dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, nslots) : dim3(nslots, p.Hq, p.B);
-  tc_fwd_kernel<T, D, HOOK, SPLIT, DROP><<<grid, NTHREADS, L::alloc, s>>>(maps, pp, device_status_word());
+  // Programmatic stream serialization: this launch may begin (CTA placement, barrier and TMEM set-up)
+  // while the previous kernel of the stream drains; the kernel waits before any global access.
+  static const bool pdl = std::getenv("FAWS_NO_PDL") == nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(NTHREADS, 1, 1);
+  cfg.dynamicSmemBytes = L::alloc;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  int* status_word = device_status_word();
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>, maps, pp, status_word);
   count_launch();
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // Few CTAs (less than two per SM with 256-row CTAs): the launch is bound by the longest chain of
