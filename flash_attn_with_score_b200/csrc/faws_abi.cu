@@ -220,6 +220,7 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   ColSoftmaxParams c = make_cs(p, f.L, sum_out, i_begin, n_end);
   if (w.scratch != nullptr) { c.s_scratch = w.scratch; c.split = buffered_split; }
   if (dropout_in_sum) c.drop = make_drop(p);
+  c.after_forward = 1;
   if (i_begin >= p->m_end) {
     // no query of the window lies beyond the split: the sums are zero
     if (cudaMemsetAsync(sum_out, 0, (size_t)p->B * (per_q_head ? p->Hq : p->Hk) * (size_t)n_end * 4, s) != cudaSuccess)

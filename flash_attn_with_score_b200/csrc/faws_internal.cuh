@@ -114,6 +114,8 @@ struct ColSoftmaxParams {
   const float* s_scratch;  // if non-null read scaled scores (B,Hq,M-split,split) instead of q.k
   int split;
   DropoutParams drop;    // p > 0: dropped weights are left out of the sum (no rescale)
+  int after_forward;     // launched right after this call's forward pass, which wrote L but not q, k:
+                         // the tcgen05 kernel may start its loads and MMAs while that pass drains
 };
 
 struct ReducePartialParams {

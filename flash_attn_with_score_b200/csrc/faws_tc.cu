@@ -179,9 +179,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // The next forward launch of the stream may place its CTAs on SMs this grid no longer needs
-  // (it waits at griddep_wait() before it touches global memory).
-  griddep_launch_dependents();
   // Launch order.  Default: row blocks fastest, so the CTAs of a head run together and share its
   // K/V through L2.  lpt_order (causal, K/V small enough to stay in L2 anyway): row blocks
   // slowest, so the heaviest row blocks of every head are dispatched first (longest-processing-
@@ -232,6 +229,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       for (int cc = 0; cc < 8; ++cc) *reinterpret_cast<uint4*>(tile + lane * 128 + (cc << 4)) = fill;
       fence_proxy_async_smem();
       griddep_wait();  // the previous kernel of the stream may still be reading or writing the scores
+      griddep_launch_dependents();
       __syncwarp();
       if (lane == 0) {
         constexpr int kGroups = CTA_ROWS / 32;
@@ -316,6 +314,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     tmem_relinquish();
   }
   griddep_wait();  // every thread, before its first global access
+  // Only now (the kernels before this one are complete) may a dependent launch begin: the key-major
+  // pass of the same call reads q and k while this grid drains, the next forward launch sets itself
+  // up on SMs this grid no longer needs.
+  griddep_launch_dependents();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1157,6 +1159,9 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
   } else {
     reg_alloc<CS_REGS_CONSUMER>();
     // ------------------------------------------------------------ consumers: thread = key
+    // L comes from the forward pass this launch may overlap (programmatic dependent launch): the
+    // consumers are the only threads that read it, and the only ones that write the result.
+    griddep_wait();
     const int wg = (warp - 4) >> 2;
     const int lg = warp & 3;
     const int row = lg * 32 + lane;
@@ -1573,9 +1578,21 @@ cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads
   }
   const int nkt = (p.n_end + BN - 1) / BN;
   dim3 grid = p.causal ? dim3(p.Hq / heads_per_cta, p.B, nkt) : dim3(nkt, p.Hq / heads_per_cta, p.B);
-  tc_colsoftmax_kernel<T, D><<<grid, CS_THREADS, L::alloc, s>>>(maps, p, heads_per_cta, device_status_word());
+  static const bool pdl = std::getenv("FAWS_NO_PDL") == nullptr;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(CS_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = L::alloc;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl && p.after_forward) ? 1 : 0;  // q and k must not come from the previous kernel
+  int* status_word = device_status_word();
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_colsoftmax_kernel<T, D>, maps, p, heads_per_cta, status_word);
   count_launch();
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 }  // namespace
 
