@@ -170,6 +170,19 @@ def cpu_reference_time(cfg, runs):
     return ts
 
 
+def check_parity(buffers, cfg):
+    """out / scores of one buffer set against the CPU oracle (the checker, outside every timed region)."""
+    from oracle import oracle as orc
+    q, k, v, out, scores = buffers
+    torch.cuda.synchronize()
+    ref_out, ref_scores = orc.naive_attention_with_scores(q.cpu(), k.cpu(), v.cpu(), cfg["causal"])
+    ok_out, out_err = orc.check_out(out.cpu(), ref_out)
+    ok_sc, viol, ok_mask = orc.check_scores(scores.cpu(), ref_scores)
+    return {"checked": True, "ok": bool(ok_out and ok_sc and ok_mask), "out_max_abs": out_err, "out_tol": orc.OUT_ATOL,
+            "scores_max_viol": viol, "scores_tol": "1e-3*|ref| + 1e-4 (violation <= 0 passes)",
+            "mask_bit_exact": bool(ok_mask), "against": "oracle/oracle.py naive_attention_with_scores, whole tensors"}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -221,7 +234,7 @@ def time_op(fn, iters, warmup):
 
 
 def ops_table(F, device, pk):
-    """The other operators on their benchmark configurations (mean ms of a few back-to-back calls)."""
+    """The other operators on their benchmark configurations (mean ms of 30 back-to-back calls each)."""
     rows = []
     cfg3 = dict(B=1, Hq=28, Hk=4, S=4096, D=128, dtype=torch.bfloat16, causal=True, vscale=0.5)
     cfg4 = dict(B=2, Hq=32, Hk=8, S=4096, D=128, dtype=torch.float16, causal=True)
@@ -244,7 +257,7 @@ def ops_table(F, device, pk):
                 call = lambda: fn(q, k, v, cfg["causal"])  # noqa: E731
             else:
                 call = lambda: fn(q, k, v, split, cfg["causal"])  # noqa: E731
-            ms = time_op(call, 5, 3 if name != "cfg5" else 1)
+            ms = time_op(call, 30, 3)
             flops, nbytes = algorithmic(cfg, "scores" if op == "attention" else op, split)
             if op == "attention":
                 nbytes -= cfg["B"] * cfg["Hq"] * cfg["S"] * cfg["S"] * 4
@@ -395,6 +408,22 @@ def main():
     total_ms = t_start.elapsed_time(t_end)
     status = F.device_status()
 
+    # What the timed region wrote, checked outside it: out and scores of the buffer set its last step used
+    # (results of the graph replay when a graph was timed) against the CPU oracle.
+    parity = check_parity(sets[(args.steps - 1) % N_SETS], cfg) if rank == 0 else None
+
+    # A steadier figure beside the K-step headline: >= 200 graph-replayed launches back to back.
+    long_ms = None
+    if graph is not None:
+        n_long = max(1, -(-200 // N_SETS))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_long):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        long_ms = a.elapsed_time(b) / (n_long * N_SETS)
+
     # per-step event times of directly launched steps (host launch cost included)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     for i in range(args.steps):
@@ -513,12 +542,15 @@ def main():
         "roofline": {"bound": "hbm", "achieved": nbytes / (launch_ms * 1e-3) / 1e9, "peak": pk["hbm"],
                      "unit": "GB/s", "frac": nbytes / (launch_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
                      "peak_source": pk["src"], "kernel": "tc_fwd_kernel<half,128> (scores hook)",
-                     "algorithmic_bytes": nbytes, "kernel_ms": launch_ms, "kernel_event_ms": kern_ms,
+                     "algorithmic_bytes": nbytes, "kernel_ms": launch_ms, "kernel_ms_long": long_ms,
+                     "frac_long": (nbytes / (long_ms * 1e-3) / 1e9 / pk["hbm"]) if long_ms else None,
+                     "kernel_event_ms": kern_ms, "frac_event": nbytes / (kern_ms * 1e-3) / 1e9 / pk["hbm"],
                      "step_event_ms": step_event_ms, "timing": launch_timing},
         "e2e": {"value": world * score_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                 "pipeline": "two buffer sets; H2D, kernel and D2H of neighbouring steps overlap on three streams"},
         "gpu_launches": launches, "backend": F.last_backend(), "device_status": status, "clocks": clocks,
+        "parity": parity,
     }
     line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
     if qsplit is not None:
@@ -532,10 +564,13 @@ def main():
                                 "sample": f"whole cfg2 problem, median of 5 calls of the naive PyTorch path "
                                           f"(oracle port), {cores} threads of {os.cpu_count()} logical CPUs"}
     if world == 1 and not args.no_ops:
+        ops_sampler = ClockSampler(local_rank)
+        ops_sampler.start()
         try:
             line["ops"] = ops_table(F, device, pk)
         except Exception as e:  # keep the headline line even if a side measurement fails
             line["ops_error"] = repr(e)
+        line["ops_clocks"] = ops_sampler.stop()
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -6,7 +6,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("FAWS_LIB_PATH") or os.path.join(HERE, "libfaws.so")  # override: ablation builds
+LIB_PATH = os.path.join(HERE, "libfaws.so")
 
 FP16, BF16 = 0, 1
 SCORES_F32, SCORES_INPUT = 0, 1
@@ -26,7 +26,8 @@ EXPORTS = [
     "faws_attention_with_col_sum_sequential",
     "faws_attention_with_softmax_col_sum", "faws_attention_cross_token_qk_sum",
     "faws_attention_cross_token_softmax_sum", "faws_attention_cross_token_softmax_sum_buffered",
-    "faws_total_attention", "faws_workspace_bytes", "faws_reduce_ranks", "faws_device_status", "faws_last_backend",
+    "faws_total_attention", "faws_workspace_bytes", "faws_reduce_ranks", "faws_device_status",
+    "faws_selftest_wait_give_up", "faws_last_backend",
     "faws_launch_count", "faws_strerror", "faws_version",
 ]
 
@@ -77,6 +78,7 @@ def load():
         "faws_workspace_bytes": (sz, [i32, PP, i32]),
         "faws_reduce_ranks": (i32, [vp, i32, C.c_int64, vp, vp]),
         "faws_device_status": (i32, [i32]),
+        "faws_selftest_wait_give_up": (i32, [vp]),
         "faws_last_backend": (i32, []),
         "faws_launch_count": (C.c_int64, []),
         "faws_strerror": (C.c_char_p, [i32]),

@@ -1,9 +1,13 @@
 """Builds libfaws.so (the C-ABI library of include/faws.h) in-tree with nvcc for sm_100a.
 
     python -m flash_attn_with_score_b200.build [--force] [--verbose]
+
+Each translation unit is compiled to an object file under build/ (in parallel, only when it is
+out of date) and the objects are linked into flash_attn_with_score_b200/libfaws.so.
 """
 from __future__ import annotations
 
+import concurrent.futures
 import os
 import subprocess
 import sys
@@ -11,9 +15,11 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.environ.get("FAWS_LIB_PATH") or os.path.join(HERE, "libfaws.so")
+OBJDIR = os.path.join(ROOT, "build", "libfaws")
+LIB = os.path.join(HERE, "libfaws.so")
 SOURCES = ["faws_abi.cu", "faws_generic.cu", "faws_tc.cu", "faws_noalloc.cu"]
-HEADERS = ["faws_internal.cuh", "faws_tc_ptx.cuh"]
+HEADERS = ["faws_internal.cuh", "faws_tc_ptx.cuh", "faws_tc_host.cuh"]
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
 def _nvcc() -> str:
@@ -23,33 +29,53 @@ def _nvcc() -> str:
     return "nvcc"
 
 
-def needs_build() -> bool:
-    if not os.path.exists(LIB):
+def _deps() -> list[str]:
+    return [os.path.join(CSRC, f) for f in HEADERS] + [os.path.join(ROOT, "include", "faws.h")]
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
         return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS] + [os.path.join(ROOT, "include", "faws.h")]
-    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in deps)
+    t = os.path.getmtime(target)
+    return any(os.path.exists(d) and os.path.getmtime(d) > t for d in sources)
+
+
+def needs_build() -> bool:
+    return _stale(LIB, [os.path.join(CSRC, f) for f in SOURCES] + _deps())
+
+
+def _compile(src: str, force: bool, verbose: bool) -> tuple[str, int, str]:
+    obj = os.path.join(OBJDIR, os.path.splitext(src)[0] + ".o")
+    path = os.path.join(CSRC, src)
+    if not force and not _stale(obj, [path] + _deps()):
+        return obj, 0, ""
+    cmd = [_nvcc(), "-c", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo"] + ARCH + [
+        "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-o", obj, path]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    return obj, res.returncode, res.stdout + res.stderr
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
-    cmd = [
-        _nvcc(), "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo",
-        "-gencode", "arch=compute_100a,code=sm_100a",
-        "-I", os.path.join(ROOT, "include"), "-I", CSRC,
-        "-o", LIB,
-    ] + [os.path.join(CSRC, s) for s in SOURCES] + ["-lcuda"]
-    if os.environ.get("FAWS_NVCC_FLAGS"):
-        cmd[1:1] = os.environ["FAWS_NVCC_FLAGS"].split()
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
+    os.makedirs(OBJDIR, exist_ok=True)
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        results = list(pool.map(lambda s: _compile(s, force, verbose), SOURCES))
+    failed = False
+    for obj, rc, log in results:
+        if verbose or rc != 0:
+            sys.stderr.write(log)
+        failed = failed or rc != 0
+    if failed:
+        raise RuntimeError("nvcc failed building libfaws.so")
+    cmd = [_nvcc(), "-shared"] + ARCH + ["-o", LIB] + [obj for obj, _, _ in results] + ["-lcuda"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libfaws.so")
+        raise RuntimeError("nvcc failed linking libfaws.so")
     return LIB
 
 

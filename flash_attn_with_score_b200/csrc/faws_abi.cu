@@ -353,6 +353,10 @@ int faws_reduce_ranks(const float* parts, int32_t n_ranks, int64_t count, float*
 
 int faws_device_status(int32_t reset) { return tc_read_status(reset); }
 
+int faws_selftest_wait_give_up(void* stream) {
+  return launch_wait_give_up(static_cast<cudaStream_t>(stream)) == cudaSuccess ? FAWS_OK : FAWS_ECUDA;
+}
+
 int faws_last_backend(void) { return t_last_backend; }
 int64_t faws_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

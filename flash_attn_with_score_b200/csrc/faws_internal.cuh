@@ -79,6 +79,7 @@ struct FwdParams {
   int split;
   int lpt_order;         // set by the tcgen05 launcher: heaviest causal row blocks of all heads first
   int fill_ctas;         // set by the tcgen05 launcher: masked score tiles are written by extra CTAs
+  int pair_tiles;        // set by the tcgen05 launcher: a CTA owns query tiles c and n_tiles-1-c (causal balance)
   int col_lin;           // column hook skips tiles that col_tile_linear() accepts (see below)
   int col_row_lo;        // max(col_row_begin, m_begin): first query row that contributes
   float* qsum;           // col_lin: (B,Hq,ceil(M/128),128) per-tile sums of the query rows, written by the
@@ -152,6 +153,7 @@ bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p);
 cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, int group_sum, cudaStream_t s);
 
 int tc_read_status(int reset);  // synchronising read of the device status word
+cudaError_t launch_wait_give_up(cudaStream_t s);  // self-test: a bounded wait that runs out
 
 constexpr int kGenericBlockM = 64;
 constexpr int kGenericBlockN = 64;

@@ -32,6 +32,7 @@
 #include <type_traits>
 
 #include "faws_internal.cuh"
+#include "faws_tc_host.cuh"
 #include "faws_tc_ptx.cuh"
 
 namespace faws {
@@ -47,32 +48,14 @@ constexpr int TMEM_COLS = 512;
 // CTA per SM); after re-allocation the total must not exceed that pool, otherwise the
 // .inc never returns.
 constexpr int REGS_LAUNCH = 168;
-#ifndef FAWS_REGS_AUX
-#define FAWS_REGS_AUX 56
-#endif
-constexpr int REGS_AUX = FAWS_REGS_AUX;
+constexpr int REGS_AUX = 56;
 constexpr int REGS_SOFTMAX = ((REGS_LAUNCH * NTHREADS - 128 * REGS_AUX) / 256) & ~7;
 static_assert(128 * REGS_AUX + 256 * REGS_SOFTMAX <= REGS_LAUNCH * NTHREADS, "setmaxnreg would block");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-#ifndef FAWS_F32X2
-#define FAWS_F32X2 1
-#endif
 #define FAWS_NEG_INF (__int_as_float(0xff800000))
 
-#ifdef FAWS_TRACE
-__device__ long long g_cta_times[4096 * 3];
-__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ long long g_trace[3 * 4096];
-#define TRACE_DECL(role) const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0); int tr_n = 0; long long* tr_buf = g_trace + (role) * 4096;
-#define TRACE(tag) do { if (tr_on && tr_n < 2040) { tr_buf[2 * tr_n] = (tag); tr_buf[2 * tr_n + 1] = clock64(); ++tr_n; } } while (0)
-#define TRACE_END() do { if (tr_on) { tr_buf[2 * tr_n] = -1; } } while (0)
-#else
-#define TRACE_DECL(role)
-#define TRACE(tag)
-#define TRACE_END()
-#endif
 
 struct TcMaps {
   CUtensorMap q, k, v, o;  // o: 32-row store boxes of the output
@@ -163,15 +146,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   using L = Smem<D, SPLIT>;
   constexpr int KV_SLOTS = L::kSlots;
   constexpr int CTA_ROWS = L::kRows;
-#ifdef FAWS_TRACE
-  const long long t_entry = clock64();
-  const int cta_lin = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (threadIdx.x == 0 && cta_lin < 4096) {
-    g_cta_times[cta_lin * 3] = gtimer();
-    unsigned smid; asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    g_cta_times[cta_lin * 3 + 2] = smid;
-  }
-#endif
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -187,22 +161,40 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   // CTA and a fill CTA that only writes the row block's never-visited key tiles; interleaved so
   // that their costs decrease together (heaviest compute block, most-masked fill block, ...).
   const int slot = (int)(p.lpt_order ? blockIdx.z : blockIdx.x);
-  const int ncb = (int)(p.lpt_order ? gridDim.z : gridDim.x) >> (p.fill_ctas ? 1 : 0);
-  const bool is_fill = p.fill_ctas && (slot & 1);
-  const int cb_slot = p.fill_ctas ? (slot >> 1) : slot;
-  const int cb_rel = is_fill ? cb_slot : ncb - 1 - cb_slot;  // heaviest (last) blocks first
-  const int m0 = p.m_begin + cb_rel * CTA_ROWS;
-  const int cb_abs = m0 / CTA_ROWS;
+  const int nslots = (int)(p.lpt_order ? gridDim.z : gridDim.x);
+  const int ncb = nslots >> (p.fill_ctas ? 1 : 0);
+  // pair_tiles: all compute CTAs come first in launch order, the fill CTAs after them
+  const bool is_fill = p.fill_ctas && (p.pair_tiles ? slot >= ncb : (slot & 1));
+  const int cb_slot = !p.fill_ctas ? slot : (p.pair_tiles ? (is_fill ? slot - ncb : slot) : (slot >> 1));
+  const int cb_rel = (is_fill || p.pair_tiles) ? cb_slot : ncb - 1 - cb_slot;  // heaviest (last) blocks first
   const int h = p.lpt_order ? blockIdx.x : blockIdx.y;
   const int b = p.lpt_order ? blockIdx.y : blockIdx.z;
   const int hk = h / p.G;
   const int bh = b * p.Hq + h;
 
+  // First row of the CTA's query tile(s).  Default: two adjacent tiles.  pair_tiles (causal): tile
+  // c from the top of the window together with tile c from its bottom, so that every CTA of the
+  // launch visits the same number of (query tile, key tile) pairs; a tile index past the middle
+  // is parked on the first row beyond the window (no rows, no key tiles).
+  int r_tile_of[2];
+  if (SPLIT) {
+    r_tile_of[0] = r_tile_of[1] = p.m_begin + cb_rel * BM;
+  } else if (p.pair_tiles) {
+    const int n_tiles = (p.m_end - p.m_begin + BM - 1) / BM;
+    const int hi_tile = n_tiles - 1 - cb_rel;
+    r_tile_of[0] = p.m_begin + cb_rel * BM;
+    r_tile_of[1] = p.m_begin + (hi_tile > cb_rel ? hi_tile : n_tiles) * BM;
+  } else {
+    r_tile_of[0] = p.m_begin + cb_rel * CTA_ROWS;
+    r_tile_of[1] = r_tile_of[0] + BM;
+  }
+  const int cb_abs = r_tile_of[0] / CTA_ROWS;  // start offset of the round-robin key-tile order
+
   // key tiles each query tile visits (0 for a tile that lies outside the row window)
   int nt_q[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int r0 = m0 + (SPLIT ? 0 : t * BM);
+    const int r0 = r_tile_of[t];
     int hi = 0;
     if (r0 < p.m_end) {
       hi = p.N;
@@ -235,9 +227,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         constexpr int kGroups = CTA_ROWS / 32;
         int unit = 0;  // (row group, column chunk) units are dealt round-robin to the 12 warps
         for (int rg = 0; rg < kGroups; ++rg) {
-          const int r0 = m0 + rg * 32;
-          if (r0 >= p.m_end) break;
           const int t = SPLIT ? 0 : rg / 4;
+          const int r0 = r_tile_of[t] + (rg & 3) * 32;
+          if (r0 >= p.m_end) continue;
           for (int j0 = nt_q[t] * BN; j0 < p.N; j0 += kCols, ++unit) {
             if (unit % 12 == warp) tma_store_3d(&maps.st, tile, j0, r0 - p.m_begin, bh);
           }
@@ -245,10 +237,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         tma_store_commit();
         tma_store_wait<0>();
       }
-#ifdef FAWS_TRACE
-      __syncthreads();
-      if (threadIdx.x == 0 && cta_lin < 4096) g_cta_times[cta_lin * 3 + 1] = gtimer();
-#endif
       return;
     }
   }
@@ -305,7 +293,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       for (int t = 0; t < L::kQTiles; ++t)
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
-                      m0 - p.m_begin + t * BM, h, b);
+                      r_tile_of[t] - p.m_begin, h, b);
       for (int idx = 0; idx < n_early; ++idx) issue_kv_load(idx);
     }
   }
@@ -354,7 +342,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
               a0 += x.x; a1 += x.y;
               b0 += y.x; b1 += y.y;
             }
-            const int r0 = m0 + t * BM;
+            const int r0 = r_tile_of[t];
             if (r0 < p.M) {
               float* dst = p.qsum + (((int64_t)bh * nqb_total + r0 / BM) * 128 + c * 64 + word * 2);
               *reinterpret_cast<float2*>(dst) = make_float2(a0 + b0, a1 + b1);
@@ -373,11 +361,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       // Operand descriptors are built once; inside the loops only compile-time offsets (in
       // 16-byte units) are added to their address field, so the issuing thread spends a few
       // instructions per MMA.
-#ifdef FAWS_TRACE
-      long long cyc_qk = 0, cyc_pv = 0, cyc_wait_p = 0, cyc_wait_kv = 0;
-      int n_qk = 0, n_pv = 0;
-      const long long c_role0 = clock64();
-#endif
       const uint64_t q_desc0 = make_desc_sw128(smem_u32(smem + L::q_off), 16, 1024);
       const uint64_t k_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), 16, 1024);
       const uint64_t v_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), L::kSub, 1024);
@@ -392,9 +375,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const uint64_t kd = k_desc0 + (uint64_t)(slot * (L::kTile >> 4));
         const uint32_t d_tmem = tmem_base + (uint32_t)(t * BN);
         if (elect_one()) {
-#ifdef FAWS_TRACE
-          const long long c0 = clock64();
-#endif
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
@@ -402,9 +382,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
             else mma_ss_acc(d_tmem, qd + off, kd + off, idesc_qk);
           }
           mma_commit(&bars->s_full[t]);
-#ifdef FAWS_TRACE
-          cyc_qk += clock64() - c0; ++n_qk;
-#endif
         }
         __syncwarp();
       };
@@ -441,18 +418,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const uint32_t d_tmem = tmem_base + 256 + (uint32_t)(t * BN);
         const uint32_t a_tmem = tmem_base + (uint32_t)(t * BN);
         if (elect_one()) {
-#ifdef FAWS_TRACE
-          const long long c0 = clock64();
-#endif
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk) {
             const uint64_t off = (uint64_t)((kk * 16 * 128) >> 4);
             if (kk == 0) mma_ts(d_tmem, a_tmem, vd, idesc_pv, accumulate ? 1u : 0u);
             else mma_ts_acc(d_tmem, a_tmem + (uint32_t)(kk * 8), vd + off, idesc_pv);
           }
-#ifdef FAWS_TRACE
-          cyc_pv += clock64() - c0; ++n_pv;
-#endif
         }
         __syncwarp();
       };
@@ -461,12 +432,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         __syncwarp();
       };
       int cnt[2] = {0, 0};  // key tiles each warpgroup has been given so far
-#ifdef FAWS_TRACE
-      const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0);
-      int tr_n = 0;
-      long long* tr_buf = g_trace + 2 * 4096;
-#endif
-      TRACE(0);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
       if constexpr (SPLIT) {
         // Visiting index `it` belongs to warpgroup it & 1.  Before S of that warpgroup is
@@ -500,22 +465,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const bool more = it + 1 < nt;
         const int tk_next = more ? tile_of(it + 1) : 0;
         const int v_slot = (2 * it + 1) % KV_SLOTS, k_slot = (2 * it + 2) % KV_SLOTS;
-        TRACE(10);
         if (!(ok = kv_wait(2 * it + 1))) break;
-        TRACE(11);
         if (tk < nt_q[0]) {
           if (!(ok = pv_when_ready(0, v_slot, cnt[0]))) break;
-          TRACE(12);
           ++cnt[0];
         }
         if (more) {
           if (!(ok = kv_wait(2 * it + 2))) break;
-          TRACE(13);
           if (tk_next < nt_q[0]) issue_qk(0, k_slot);
         }
         if (tk < nt_q[1]) {
           if (!(ok = pv_when_ready(1, v_slot, cnt[1]))) break;
-          TRACE(14);
           ++cnt[1];
         }
         commit(&bars->kv_empty[v_slot]);
@@ -526,21 +486,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
       }  // !SPLIT
       if (ok) commit(&bars->o_done);
-#ifdef FAWS_TRACE
-      // the elected lane differs from lane 0 in general: reduce the counters over the warp
-      for (int o = 16; o > 0; o >>= 1) {
-        cyc_qk += __shfl_xor_sync(0xffffffffu, cyc_qk, o);
-        cyc_pv += __shfl_xor_sync(0xffffffffu, cyc_pv, o);
-        n_qk += __shfl_xor_sync(0xffffffffu, n_qk, o);
-        n_pv += __shfl_xor_sync(0xffffffffu, n_pv, o);
-      }
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) {
-        g_trace[2 * 4096 + 4000] = cyc_qk; g_trace[2 * 4096 + 4001] = n_qk;
-        g_trace[2 * 4096 + 4002] = cyc_pv; g_trace[2 * 4096 + 4003] = n_pv;
-        g_trace[2 * 4096 + 4004] = clock64() - c_role0;
-      }
-#endif
-      TRACE_END();
     }
   } else {
     reg_alloc<REGS_SOFTMAX>();
@@ -548,7 +493,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     const int qt = (warp - 4) >> 2;  // warpgroup: its query tile (or, SPLIT, its half of the key tiles)
     const int lg = warp & 3;         // TMEM lane group this warp may touch
     const int row = lg * 32 + lane;
-    const int r_tile = m0 + (SPLIT ? 0 : qt * BM);  // first row of the query tile
+    const int r_tile = r_tile_of[qt];  // first row of the query tile
     const int i = r_tile + row;
     const int my_nt = nt_q[qt];
     const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
@@ -571,13 +516,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
     bool alive = true;
     int hook_cnt = 0;  // column hook executions (selects its smem buffer and barrier phase)
-#ifdef FAWS_TRACE
-    const bool tr_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0);
-    int tr_n = 0;
-    long long* tr_buf = g_trace + qt * 4096;
-    if (tr_on) { tr_buf[0] = 99; tr_buf[1] = t_entry; tr_n = 1; }
-    TRACE(1);
-#endif
 
     // One key tile.  The row's 128 scores are read from TMEM once and stay in registers: first
     // for the max and exp2 passes (the chain the tensor pipe waits on), then, after P has been
@@ -588,7 +526,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
       tmem_wait_ld();
-      TRACE(21);
       int nvis = 128;  // visible columns form a prefix of the tile's row
       if (kMasked) {
         int lim = p.N;
@@ -607,7 +544,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         a3 = fmaxf(a3, FAWS_VIS(x + 3) ? __uint_as_float(r[x + 3]) : FAWS_NEG_INF);
       }
       const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * scale_log2;  // sm_scale > 0
-      TRACE(22);
 
       // ---- running max, lazy rescale of O.  s_full for this tile was committed after this
       // query tile's previous P.V MMA, so O_t is quiescent here.
@@ -630,23 +566,19 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           tmem_st32(t_o + c * 32, ro);
         }
       }
-      TRACE(23);
 
       // ---- P = exp2(s*scale*log2e - m), row sum of P, P -> TMEM over S as 16-bit pairs
       const float neg_m = (m_run == FAWS_NEG_INF) ? 0.f : -m_run;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#if FAWS_F32X2
       const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
       const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
       uint64_t lp0 = 0ull, lp1 = 0ull;
-#endif
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float e[8];
-#if FAWS_F32X2
           // packed 2 x fp32 FMA / ADD: half the FMA-pipe instructions of the scalar form
 #pragma unroll
           for (int y = 0; y < 8; y += 2) {
@@ -658,18 +590,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           }
           lp0 = add_f32x2(lp0, add_f32x2(pack_f32x2(e[0], e[1]), pack_f32x2(e[4], e[5])));
           lp1 = add_f32x2(lp1, add_f32x2(pack_f32x2(e[2], e[3]), pack_f32x2(e[6], e[7])));
-#else
-#pragma unroll
-          for (int y = 0; y < 8; ++y) {
-            const int x = c * 32 + g * 8 + y;
-            const float pe = fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, neg_m));
-            e[y] = FAWS_VIS(x) ? pe : 0.f;
-          }
-          l0 += e[0] + e[4];
-          l1 += e[1] + e[5];
-          l2 += e[2] + e[6];
-          l3 += e[3] + e[7];
-#endif
           if constexpr (DROP) {
             // dropout acts on the weights that multiply V only; the row sums above are taken
             // before it (flash.py:459-466)
@@ -690,16 +610,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           mbar_arrive(&bars->p_half[qt]);
         }
       }
-      TRACE(24);
       tmem_wait_st();
-#if FAWS_F32X2
       unpack_f32x2(lp0, l0, l1);
       unpack_f32x2(lp1, l2, l3);
-#endif
       l_run += (l0 + l1) + (l2 + l3);
       tc_fence_before();
       mbar_arrive(&bars->p_ready[qt]);
-      TRACE(25);
 
       // ---- score-tile hooks: off the chain above, they overlap this tile's P.V MMA
       if constexpr (HOOK == kHookRowSum) {
@@ -820,7 +736,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         }
       }
 #undef FAWS_VIS
-      TRACE(26);
       return true;
     };
 
@@ -868,9 +783,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const int tk = tile_of(it);
         if (SPLIT ? ((it & 1) != qt) : (tk >= my_nt)) continue;
         const int n0 = tk * BN;
-        TRACE(19);
         if (!mbar_wait(&bars->s_full[qt], cnt & 1, abort_flag)) { alive = false; break; }
-        TRACE(20);
         tc_fence_after();
         const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= r_tile + p.p_seq));
         const bool ok = full_vis ? tile_body(std::false_type{}, cnt, n0) : tile_body(std::true_type{}, cnt, n0);
@@ -885,7 +798,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       if (!mbar_wait(&bars->o_done, 0, abort_flag)) alive = false;
       tc_fence_after();
     }
-    TRACE(30);
     // SPLIT: warpgroup 1 publishes its running state; warpgroup 0 merges the two partial results.
     float* merge = reinterpret_cast<float*>(smem + L::kv_off);  // ring is free after o_done
     bool write_out = alive && r_tile < p.m_end;
@@ -973,12 +885,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs_all;
       }
     }
-    TRACE(31);
     // Full completion, not only the reads: measured on the score-materialising launches, CTAs that leave
     // while their stores are still draining make the launch 4 % slower; no difference elsewhere.
     if (lane < 2) tma_store_wait<0>();
-    TRACE(32);
-    TRACE_END();
   }
 
   // ------------------------------------------------------------ common exit
@@ -994,9 +903,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-#ifdef FAWS_TRACE
-  if (threadIdx.x == 0 && cta_lin < 4096) g_cta_times[cta_lin * 3 + 1] = gtimer();
-#endif
 }
 
 // ---------------------------------------------------------------------------- key-major pass
@@ -1011,18 +917,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 // CS_WGS = 4 consumer warpgroups (16 warps, 4 per scheduler): warpgroup w owns S^T buffer w and Q
 // slot w, takes every fourth query tile in chunks of CS_CHUNK columns (that many live score
 // registers), and the partial sums are added in a fixed order at the end.
-#ifndef FAWS_CS_WGS
-#define FAWS_CS_WGS 4
-#endif
-#ifndef FAWS_CS_CHUNK
-#define FAWS_CS_CHUNK 64
-#endif
-#ifndef FAWS_CS_F32X2
-#define FAWS_CS_F32X2 FAWS_F32X2
-#endif
-constexpr int CS_WGS = FAWS_CS_WGS;
+constexpr int CS_WGS = 4;
 constexpr int CS_QSLOTS = CS_WGS;
-constexpr int CS_CHUNK = FAWS_CS_CHUNK;  // score columns a consumer thread holds at a time
+constexpr int CS_CHUNK = 64;  // score columns a consumer thread holds at a time
 constexpr int CS_THREADS = 128 + CS_WGS * 128;
 constexpr int CS_REGS_LAUNCH = (65536 / CS_THREADS) & ~7;  // what the launch bound lets ptxas allocate
 constexpr int CS_REGS_AUX = 56;
@@ -1184,10 +1081,6 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 
     bool alive = true;
     int mine = 0;  // tiles this warpgroup has processed
-#ifdef FAWS_TRACE
-    long long cs_wait_l = 0, cs_wait_s = 0, cs_ld = 0, cs_comp = 0; int cs_tiles = 0;
-    const long long cs_t0 = clock64();
-#endif
     float negl_next = (wg < total) ? load_negl(wg) : FAWS_NEG_INF;
     for (int u = wg; u < total; u += CS_WGS, ++mine) {
       // Two L buffers per warpgroup: the barrier below completes only when every thread of the
@@ -1196,18 +1089,8 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       lb[row] = negl_next;
       mbar_arrive(&bars->l_ready[wg]);
       if (u + CS_WGS < total) negl_next = load_negl(u + CS_WGS);
-#ifdef FAWS_TRACE
-      const long long cw0 = clock64();
-#endif
       if (!mbar_wait(&bars->l_ready[wg], mine & 1, abort_flag)) { alive = false; break; }
-#ifdef FAWS_TRACE
-      const long long cw1 = clock64();
-#endif
       if (!mbar_wait(&bars->s_full[wg], mine & 1, abort_flag)) { alive = false; break; }
-#ifdef FAWS_TRACE
-      const long long cw2 = clock64();
-      cs_wait_l += cw1 - cw0; cs_wait_s += cw2 - cw1; ++cs_tiles;
-#endif
       tc_fence_after();
       const int g = u / ntq, qt = qt0 + (u - g * ntq);
       const int i0 = qt * BM;
@@ -1217,9 +1100,6 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BM; c0 += CS_CHUNK) {
-#ifdef FAWS_TRACE
-        const long long ch0 = clock64();
-#endif
         uint32_t r[CS_CHUNK];
 #pragma unroll
         for (int c = 0; c < CS_CHUNK; c += 32)
@@ -1229,13 +1109,8 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           tc_fence_before();
           mbar_arrive(&bars->s_free[wg]);
         }
-#ifdef FAWS_TRACE
-        const long long ch1 = clock64();
-        cs_ld += ch1 - ch0;
-#endif
         const float* lh = lb + c0;
         if (full) {
-#if FAWS_CS_F32X2
           const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
           uint64_t ap0 = pack_f32x2(a0, a1), ap1 = pack_f32x2(a2, a3);
 #pragma unroll
@@ -1251,16 +1126,6 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           }
           unpack_f32x2(ap0, a0, a1);
           unpack_f32x2(ap1, a2, a3);
-#else
-#pragma unroll
-          for (int x = 0; x < CS_CHUNK; x += 4) {
-            const float4 nl = *reinterpret_cast<const float4*>(lh + x);
-            a0 += fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x));
-            a1 += fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y));
-            a2 += fast_exp2(fmaf(__uint_as_float(r[x + 2]), scale_log2, nl.z));
-            a3 += fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w));
-          }
-#endif
         } else {
           const int xh = xlo - c0;
 #pragma unroll
@@ -1272,19 +1137,9 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
             a3 += (x + 3 >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x + 3]), scale_log2, nl.w)) : 0.f;
           }
         }
-#ifdef FAWS_TRACE
-        cs_comp += clock64() - ch1;
-#endif
       }
       acc += (a0 + a1) + (a2 + a3);
     }
-#ifdef FAWS_TRACE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lg == 0 && lane == 0 && wg < 2) {
-      long long* o = g_trace + 2 * 4096 + 4020 + wg * 4;
-      o[0] = cs_wait_l; o[1] = cs_wait_s; o[2] = cs_tiles; o[3] = clock64() - cs_t0;
-      g_trace[2 * 4096 + 4030 + wg * 2] = cs_ld; g_trace[2 * 4096 + 4031 + wg * 2] = cs_comp;
-    }
-#endif
     if (!alive) acc = 0.f;
     if (wg > 0) comb[(wg - 1) * 128 + row] = acc;
   }
@@ -1314,81 +1169,16 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 }
 
 // ---------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
-// (rows, 64 x 16-bit) boxes out of a (B, H, S, D) view
-bool make_map_bhsd(CUtensorMap* m, const void* base, int D, int rows, int H, int B, int64_t ss, int64_t sh,
-                   int64_t sb, int box_rows) {
-  EncodeTiledFn enc = get_encode();
-  if (enc == nullptr) return false;
-  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
-  const cuuint64_t row_bytes = (cuuint64_t)ss * 2;
-  cuuint64_t strides[3] = {row_bytes, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
-  if (H == 1) strides[1] = row_bytes * (cuuint64_t)rows;
-  if (B == 1) strides[2] = strides[1] * (cuuint64_t)H;
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
-// 32 x 32 fp32 boxes into a (BH, rows, cols) tensor whose rows are `row_stride` floats apart
-// (esize = 2: 32-row x 64-column boxes of 16-bit elements, same 128-byte box rows)
-bool make_map_store_f32(CUtensorMap* m, void* base, int cols, int rows, int64_t row_stride,
-                        int64_t bh_stride, int BH, int esize = 4) {
-  EncodeTiledFn enc = get_encode();
-  if (enc == nullptr) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)row_stride * esize, (cuuint64_t)bh_stride * esize};
-  cuuint32_t box[3] = {(cuuint32_t)(128 / esize), 32, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(m, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, base, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
-bool ok16(const void* ptr, int64_t a, int64_t b, int64_t c) {
-  return (reinterpret_cast<uintptr_t>(ptr) % 16 == 0) && a % 8 == 0 && b % 8 == 0 && c % 8 == 0;
-}
-
-bool device_is_sm100() {
-  static int cached = -1;
-  if (cached < 0) {
-    int dev = 0, major = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return false;
-    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return false;
-    cached = (major == 10) ? 1 : 0;
-  }
-  return cached == 1;
-}
-
 // Per-device status word the kernels raise when a bounded wait gives up.
 __device__ int g_tc_status = 0;
 
-int* device_status_word() {
-  static int* words[64] = {nullptr};
+}  // namespace
+
+int* tc_status_word() {
+  static int* words[kMaxDevices] = {nullptr};
   static std::mutex mu;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  const int dev = current_device();
+  if (dev < 0) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   if (words[dev] == nullptr) {
     void* ptr = nullptr;
@@ -1397,16 +1187,14 @@ int* device_status_word() {
   return words[dev];
 }
 
+namespace {
+
 template <typename T, int D, int HOOK, bool SPLIT, bool DROP = false>
 cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
   using L = Smem<D, SPLIT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (cudaError_t e = set_max_smem_once(attr_once, tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>, L::alloc); e != cudaSuccess)
+    return e;
   const int ncb = (p.m_end - p.m_begin + L::kRows - 1) / L::kRows;
   FwdParams pp = p;
   // K and V of all heads together stay resident in the 126 MB L2 -> order CTAs for load balance
@@ -1414,11 +1202,24 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   pp.lpt_order = (p.causal && kv_bytes <= (48LL << 20) && 2 * ncb <= 65535) ? 1 : 0;
   // masked key tiles exist (causal, some row block ends before N): give them their own CTAs
   pp.fill_ctas = ((HOOK == kHookScores || HOOK == kHookScores16) && p.causal && p.p_seq + p.m_begin + 128 < p.N) ? 1 : 0;
+  // Causal launches whose CTAs all fit on the GPU at once, or fill whole waves: pair light and heavy
+  // query tiles so that every CTA has the same length.  With uneven last waves the heaviest-first
+  // order of unequal CTAs packs better.
+  if (!SPLIT && p.causal && ncb >= 2) {
+    const long long ctas = (long long)ncb * p.Hq * p.B;
+    const int sms = sm_count();
+    const long long waves = (ctas + sms - 1) / sms;
+    pp.pair_tiles = (ctas <= sms || (double)(waves * sms) / (double)ctas <= 1.03) ? 1 : 0;
+    static const int forced_pair = [] {  // FAWS_PAIR_TILES=0/1 overrides the choice (tests)
+      const char* e = std::getenv("FAWS_PAIR_TILES");
+      return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+    }();
+    if (forced_pair >= 0) pp.pair_tiles = forced_pair;
+  }
   const int nslots = pp.fill_ctas ? 2 * ncb : ncb;
   dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, nslots) : dim3(nslots, p.Hq, p.B);
   // Programmatic stream serialization: this launch may begin (CTA placement, barrier and TMEM set-up)
   // while the previous kernel of the stream drains; the kernel waits before any global access.
-  static const bool pdl = std::getenv("FAWS_NO_PDL") == nullptr;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(NTHREADS, 1, 1);
@@ -1428,8 +1229,8 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  int* status_word = device_status_word();
+  cfg.numAttrs = 1;
+  int* status_word = tc_status_word();
   const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>, maps, pp, status_word);
   count_launch();
   return e != cudaSuccess ? e : cudaGetLastError();
@@ -1444,8 +1245,7 @@ bool use_split_kv(const FwdParams& p) {
     return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
   }();
   if (forced >= 0) return forced == 1;
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const long long ctas256 = (long long)((p.m_end - p.m_begin + 255) / 256) * p.Hq * p.B;
   return ctas256 < 2LL * sms;
 }
@@ -1525,17 +1325,35 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
   return p.D == 128 ? launch_fwd_t<__nv_bfloat16, 128>(maps, p, s) : launch_fwd_t<__nv_bfloat16, 64>(maps, p, s);
 }
 
-#ifdef FAWS_TRACE
-extern "C" int faws_debug_read_cta_times(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_cta_times, sizeof(long long) * n);
+
+namespace {
+// Exercises the give-up path of mbar_wait: one thread waits (bounded, about a millisecond) on an
+// mbarrier nobody arrives at, the wait runs out, the CTA raises the status word and returns.
+__global__ void wait_give_up_kernel(int* __restrict__ status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, limit_cycles);
+  __syncthreads();
+  if (abort_flag != 0 && threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
 }
-extern "C" int faws_debug_read_trace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n);
+}  // namespace
+
+cudaError_t launch_wait_give_up(cudaStream_t s) {
+  int* status_word = tc_status_word();
+  if (status_word == nullptr) return cudaErrorInvalidDevice;
+  wait_give_up_kernel<<<1, 32, 0, s>>>(status_word, 2000000ll);
+  count_launch();
+  return cudaGetLastError();
 }
-#endif
 
 int tc_read_status(int reset) {
-  int* word = device_status_word();
+  int* word = tc_status_word();
   if (word == nullptr) return -1;
   int v = 0;
   if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
@@ -1548,8 +1366,7 @@ int tc_read_status(int reset) {
 // more CTAs, which matters for causal problems where the key tiles' work is very uneven.
 bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p) {
   if (p.G == 1) return true;
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const long long ctas = (long long)((p.n_end + BN - 1) / BN) * p.Hk * p.B;
   return !(p.causal && ctas < 8LL * sms) && ctas >= 2LL * sms;
 }
@@ -1569,16 +1386,10 @@ namespace {
 template <typename T, int D>
 cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads_per_cta, cudaStream_t s) {
   using L = CsSmem<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e =
-        cudaFuncSetAttribute(tc_colsoftmax_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::alloc);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static PerDeviceOnce attr_once;
+  if (cudaError_t e = set_max_smem_once(attr_once, tc_colsoftmax_kernel<T, D>, L::alloc); e != cudaSuccess) return e;
   const int nkt = (p.n_end + BN - 1) / BN;
   dim3 grid = p.causal ? dim3(p.Hq / heads_per_cta, p.B, nkt) : dim3(nkt, p.Hq / heads_per_cta, p.B);
-  static const bool pdl = std::getenv("FAWS_NO_PDL") == nullptr;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(CS_THREADS, 1, 1);
@@ -1588,8 +1399,8 @@ cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = (pdl && p.after_forward) ? 1 : 0;  // q and k must not come from the previous kernel
-  int* status_word = device_status_word();
+  cfg.numAttrs = p.after_forward ? 1 : 0;  // q and k must not come from the previous kernel
+  int* status_word = tc_status_word();
   const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_colsoftmax_kernel<T, D>, maps, p, heads_per_cta, status_word);
   count_launch();
   return e != cudaSuccess ? e : cudaGetLastError();

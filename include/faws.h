@@ -239,6 +239,14 @@ int faws_reduce_ranks(const float* parts, int32_t n_ranks, int64_t count, float*
  */
 int faws_device_status(int32_t reset);
 
+/*
+ * Self-test of that give-up path: launches one tiny kernel whose only thread waits, with a limit
+ * of about a millisecond, on an mbarrier nobody arrives at.  The wait runs out, the kernel raises
+ * the status word and returns normally (nothing faults, nothing hangs); faws_device_status then
+ * reads 1.  No counterpart in the reference.
+ */
+int faws_selftest_wait_give_up(void* stream);
+
 /* Which kernel family the calling thread's last successful call used
  * (FAWS_BACKEND_GENERIC or FAWS_BACKEND_TCGEN05; 0 before any call) and how
  * many kernels this library has launched from this process. */

@@ -81,3 +81,16 @@ def test_python_asserts_mirror_reference():
         "attention", "attention_with_scores", "attention_with_col_sum", "attention_with_col_sum_sequential",
         "attention_with_softmax_col_sum", "attention_cross_token_softmax_sum",
         "attention_cross_token_softmax_sum_buffered", "attention_with_row_sum", "attention_cross_token_qk_sum"}
+
+
+def test_reference_import_name():
+    """The reference's own import line (its README.md:27) resolves to this implementation."""
+    import flash_attention_with_scores as R
+    import flash_attn_with_score_b200 as F
+    from flash_attention_with_scores import attention_with_scores  # noqa: F401
+    names = ["attention", "attention_with_scores", "attention_with_col_sum", "attention_with_col_sum_sequential",
+             "attention_with_softmax_col_sum", "attention_cross_token_softmax_sum",
+             "attention_cross_token_softmax_sum_buffered", "attention_with_row_sum", "attention_cross_token_qk_sum"]
+    assert list(R.__all__) == names  # order of the reference's __init__.py:29-39
+    for n in names:
+        assert getattr(R, n) is getattr(F, n)

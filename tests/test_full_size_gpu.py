@@ -39,6 +39,9 @@ def _sampled_rows_oracle(q, k, v, causal, rows, b, h):
     return w @ vv, s, w, vv
 
 
+RAW_BF16_ERR = {}  # test label -> (largest raw |out - ref|, largest slack used), printed for the record
+
+
 def _check_rows(out, q, k, v, causal, what):
     S = q.shape[2]
     rows = [0, 1, 127, 128, S // 2 - 1, S // 2, S - 2, S - 1]
@@ -46,9 +49,18 @@ def _check_rows(out, q, k, v, causal, what):
         ref, s, w, vv = _sampled_rows_oracle(q, k, v, causal, rows, b, h)
         got = out[b, h, rows].float().cpu()
         tol = torch.full_like(ref, orc.OUT_ATOL)
+        err = (got - ref).abs()
         if out.dtype == torch.bfloat16:
-            tol = tol + ref.abs() * 2.0 ** -8 + (w @ vv.abs()) * 2.0 ** -9
-        assert ((got - ref).abs() <= tol).all(), (what, b, h, (got - ref).abs().max().item())
+            slack = ref.abs() * 2.0 ** -8 + (w @ vv.abs()) * 2.0 ** -9
+            tol = tol + slack
+            # on record: how far the raw bf16 error is from the plain 2e-3 bound, and how much of
+            # the bf16 allowance the kernel actually uses
+            old = RAW_BF16_ERR.get(what, (0.0, 0.0))
+            RAW_BF16_ERR[what] = (max(old[0], err.max().item()), max(old[1], (err - orc.OUT_ATOL).clamp(min=0).max().item()))
+            print(f"[bf16 out] {what} (b={b}, h={h}): raw max |out-ref| = {err.max().item():.3e} "
+                  f"(plain bound {orc.OUT_ATOL:.0e}; bf16 half-ulp at max|ref|={ref.abs().max().item():.2f} is "
+                  f"{ref.abs().max().item() * 2.0 ** -9:.3e}); allowance max {slack.max().item():.3e}")
+        assert (err <= tol).all(), (what, b, h, err.max().item())
 
 
 def _rel_rms_ok(x, ref, what):
@@ -129,3 +141,79 @@ def test_cfg5_full_size_noncausal():
     _, cs = F.attention_with_col_sum(q, k, v, False, per_q_head=True)
     _rel_rms_ok(cs[0, :4], orc.linear_col_sum(q[:1, :4], k[:1, :1], False), "cfg5 col_sum identity")
     assert F.device_status() == 0
+
+
+# ------------------------------------------------------------------ the two score-materialising configurations
+def _cfg_cpu_inputs(name):
+    cfg = orc.CONFIGS[name]
+    g = torch.Generator().manual_seed(0)
+    B, Hq, Hk, S, D = cfg["B"], cfg["Hq"], cfg["Hk"], cfg["S"], cfg["D"]
+    q = torch.randn(B, Hq, S, D, generator=g)  # fp32 draw, then the cast the GPU run receives
+    k = torch.randn(B, Hk, S, D, generator=g)
+    v = torch.randn(B, Hk, S, D, generator=g)
+    return q.half(), k.half(), v.half()
+
+
+def _check_scores_and_out(out, scores, ref_out, ref_scores, what):
+    ok, err = orc.check_out(out.cpu(), ref_out)
+    assert ok, f"{what}: out max abs err {err}"
+    ok, viol, ok_mask = orc.check_scores(scores.cpu(), ref_scores)
+    assert ok_mask, f"{what}: hidden entries are not exactly the oracle's -inf set"
+    assert ok, f"{what}: scores violation {viol}"
+    hidden = torch.isneginf(ref_scores)
+    bits = scores.cpu().view(torch.int32)[hidden]
+    assert bool((bits == orc.NEG_INF_BITS - (1 << 32)).all()), f"{what}: fill is not 0xFF800000"
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2"])
+def test_cfg1_cfg2_whole_tensor_against_oracle(name):
+    """cfg1 (B1 H8 S512 D64) and cfg2 (B1 H32 S1024 D128), causal, fp16 inputs cast from an fp32
+    draw with seed 0: the whole out and the whole fp32 score tensor against the CPU oracle."""
+    cfg = orc.CONFIGS[name]
+    q, k, v = _cfg_cpu_inputs(name)
+    ref_out, ref_scores = orc.naive_attention_with_scores(q, k, v, True)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    out, scores = F.attention_with_scores(qd, kd, vd, True)
+    assert F.last_backend() == "tcgen05"
+    assert scores.shape == (cfg["B"], cfg["Hq"], cfg["S"], cfg["S"]) and scores.dtype == torch.float32
+    _check_scores_and_out(out, scores, ref_out, ref_scores, name)
+
+    # caller-owned buffers (the call bench.py times), poisoned before every use
+    out_b = torch.full_like(qd, float("nan"))
+    sc_b = torch.full_like(scores, float("nan"))
+    o2, s2 = F.attention_with_scores(qd, kd, vd, True, out=out_b, scores=sc_b)
+    assert o2.data_ptr() == out_b.data_ptr() and s2.data_ptr() == sc_b.data_ptr()
+    _check_scores_and_out(out_b, sc_b, ref_out, ref_scores, name + " out=/scores=")
+    assert torch.equal(out_b, out) and torch.equal(sc_b.view(torch.int32), scores.view(torch.int32))
+
+    # the same call captured in a CUDA graph and replayed onto poisoned buffers
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        F.attention_with_scores(qd, kd, vd, True, out=out_b, scores=sc_b)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        out_b.fill_(float("nan"))
+        sc_b.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        _check_scores_and_out(out_b, sc_b, ref_out, ref_scores, name + " graph replay")
+    assert F.device_status() == 0
+
+    # every other score-free product of the same inputs, derived from the oracle's score tensor
+    o, rs = F.attention_with_row_sum(qd, kd, vd, True)
+    _rel_rms_ok(rs, orc.row_sum(ref_scores), name + " row_sum")
+    o, cs = F.attention_with_col_sum(qd, kd, vd, True)
+    _rel_rms_ok(cs, orc.group_sum(orc.col_sum(ref_scores), cfg["Hk"]), name + " col_sum")
+    ok, err = orc.check_out(o.cpu(), ref_out)
+    assert ok, err
+    o, sc = F.attention_with_softmax_col_sum(qd, kd, vd, True)
+    _rel_rms_ok(sc, orc.group_sum(orc.softmax_col_sum(ref_scores), cfg["Hk"]), name + " softmax_col_sum")
+    assert F.device_status() == 0
+
+
+def test_bf16_raw_error_report():
+    """Runs after the cfg3 / cfg5 tests of this file: prints the raw bf16 errors they recorded."""
+    for what, (raw, over) in sorted(RAW_BF16_ERR.items()):
+        print(f"[bf16 out summary] {what}: raw max abs err {raw:.3e}, above the plain 2e-3 bound by {over:.3e}")
