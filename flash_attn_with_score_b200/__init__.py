@@ -11,6 +11,7 @@ from .api import (  # noqa: F401
     attention_with_row_sum,
     attention_with_scores,
     attention_with_softmax_col_sum,
+    compute_attention_scores,
     device_status,
     last_backend,
     launch_count,
@@ -28,4 +29,5 @@ __all__ = [
     "attention_with_row_sum",
     "attention_cross_token_qk_sum",
     "total_attention",
+    "compute_attention_scores",
 ]

@@ -18,15 +18,18 @@ BACKENDS = {None: BACKEND_AUTO, "auto": BACKEND_AUTO, "generic": BACKEND_GENERIC
 OP_ATTENTION, OP_SCORES, OP_ROW_SUM, OP_COL_SUM, OP_COL_SUM_SEQUENTIAL = 0, 1, 2, 3, 4
 OP_SOFTMAX_COL_SUM, OP_CROSS_QK_SUM, OP_CROSS_SOFTMAX_SUM, OP_CROSS_SOFTMAX_SUM_BUFFERED = 5, 6, 7, 8
 OP_TOTAL_ATTENTION = 9
+OP_ATTENTION_BACKWARD = 10
+OP_ATTENTION_SPLIT_KV = 11
 
 # every symbol include/faws.h declares
 EXPORTS = [
-    "faws_attention", "faws_attention_with_scores", "faws_attention_with_row_sum",
+    "faws_attention", "faws_attention_with_scores", "faws_compute_attention_scores", "faws_split_kv_plan",
+    "faws_attention_split_kv", "faws_attention_with_row_sum",
     "faws_attention_with_col_sum", "faws_attention_with_col_sum_noalloc",
     "faws_attention_with_col_sum_sequential",
     "faws_attention_with_softmax_col_sum", "faws_attention_cross_token_qk_sum",
     "faws_attention_cross_token_softmax_sum", "faws_attention_cross_token_softmax_sum_buffered",
-    "faws_total_attention", "faws_workspace_bytes", "faws_reduce_ranks", "faws_device_status",
+    "faws_total_attention", "faws_attention_backward", "faws_workspace_bytes", "faws_reduce_ranks", "faws_device_status",
     "faws_selftest_wait_give_up", "faws_last_backend",
     "faws_launch_count", "faws_strerror", "faws_version",
 ]
@@ -48,6 +51,10 @@ class Problem(C.Structure):
     ]
 
 
+class Grads(C.Structure):
+    _fields_ = [("dout", Tensor), ("dq", Tensor), ("dk", Tensor), ("dv", Tensor)]
+
+
 _lib = None
 
 
@@ -66,6 +73,9 @@ def load():
     protos = {
         "faws_attention": (i32, [PP, vp]),
         "faws_attention_with_scores": (i32, [PP, vp, i32, u32, vp]),
+        "faws_compute_attention_scores": (i32, [PP, vp, i32, vp]),
+        "faws_split_kv_plan": (i32, [PP]),
+        "faws_attention_split_kv": (i32, [PP, i32, vp, sz, vp]),
         "faws_attention_with_row_sum": (i32, [PP, vp, vp]),
         "faws_attention_with_col_sum": (i32, [PP, vp, i32, vp, sz, vp]),
         "faws_attention_with_col_sum_noalloc": (i32, [PP, vp, i32, vp]),
@@ -75,6 +85,7 @@ def load():
         "faws_attention_cross_token_softmax_sum": (i32, [PP, i32, vp, i32, vp, sz, vp]),
         "faws_attention_cross_token_softmax_sum_buffered": (i32, [PP, i32, vp, i32, vp, sz, vp]),
         "faws_total_attention": (i32, [PP, vp, vp]),
+        "faws_attention_backward": (i32, [PP, C.POINTER(Grads), vp, sz, vp]),
         "faws_workspace_bytes": (sz, [i32, PP, i32]),
         "faws_reduce_ranks": (i32, [vp, i32, C.c_int64, vp, vp]),
         "faws_device_status": (i32, [i32]),

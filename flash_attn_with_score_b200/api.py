@@ -134,26 +134,78 @@ def _f32_bits(x: float) -> int:
     return struct.unpack("<I", struct.pack("<f", x))[0]
 
 
+def _attention_forward(q, k, v, causal, sm_scale, dropout_p, need_L, want_total, q_rows, backend, philox,
+                       kv_splits=None):
+    c = _Call(q, k, v, causal, sm_scale, dropout_p, need_L=need_L, q_rows=q_rows, backend=backend,
+              philox=philox, rescale=True)
+    # few query rows (decoding): split the keys over more CTAs, as flash.py:68-70,97-134 does
+    n_splits = int(c.lib.faws_split_kv_plan(C.byref(c.p))) if kv_splits is None else int(kv_splits)
+    if n_splits > 1:
+        ws, n = c.workspace(_lib.OP_ATTENTION_SPLIT_KV, n_splits)
+        c.run("faws_attention_split_kv", n_splits, C.c_void_p(ws.data_ptr()), n)
+    else:
+        c.run("faws_attention")
+    tot = None
+    if want_total:
+        tot = torch.empty((c.B, c.H, c.N), device=c.dev, dtype=torch.float32)
+        c.run("faws_total_attention", C.c_void_p(tot.data_ptr()))
+    return c, tot
+
+
+class _AttentionFunction(torch.autograd.Function):
+    """attention() under autograd: the reference's FlashAttention (flash.py:32-261).  Saves
+    (q, k, v, out, log-normaliser) like flash.py:152; backward runs faws_attention_backward."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, dropout_p, want_total, backend, philox, kv_splits):
+        c, tot = _attention_forward(q, k, v, causal, sm_scale, dropout_p, True, want_total, None, backend, philox,
+                                    kv_splits)
+        ctx.save_for_backward(c.q, c.k, c.v, c.out, c.L)
+        ctx.causal, ctx.sm_scale, ctx.dropout_p, ctx.backend = causal, float(c.p.sm_scale), dropout_p, backend
+        ctx.philox = (c.seed, c.offset) if c.seed is not None else None
+        ctx.mark_non_differentiable(c.L)
+        if tot is not None:
+            ctx.mark_non_differentiable(tot)
+        return c.out, c.L, tot, c.seed, c.offset
+
+    @staticmethod
+    def backward(ctx, do, *ignored):
+        q, k, v, o, L = ctx.saved_tensors
+        do = maybe_contiguous(do)
+        c = _Call(q, k, v, ctx.causal, ctx.sm_scale, ctx.dropout_p, out=o, L=L, backend=ctx.backend,
+                  philox=ctx.philox, rescale=True)
+        dq, dk, dv = torch.empty_like(c.q), torch.empty_like(c.k), torch.empty_like(c.v)
+        g = _lib.Grads(_tensor(do), _tensor(dq), _tensor(dk), _tensor(dv))
+        ws, n = c.workspace(_lib.OP_ATTENTION_BACKWARD)
+        c.run("faws_attention_backward", C.byref(g), C.c_void_p(ws.data_ptr()), n)
+        return dq, dk, dv, None, None, None, None, None, None, None
+
+
 def attention(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
               return_log_normalizer=False, return_total_attention=False, return_seed_offset=False,
-              *, q_rows=None, backend=None, philox=None):
-    """FlashAttention forward; the reference's ``attention`` (flash.py:264-295), forward only.
+              *, q_rows=None, backend=None, philox=None, kv_splits=None):
+    """FlashAttention; the reference's ``attention`` (flash.py:264-295), differentiable in q, k, v
+    like the reference's autograd function (flash.py:32-261).  Problems with few query rows are run
+    split-KV like there (flash.py:68-70); ``kv_splits`` pins the number of key ranges (1 = never).
 
     Returns ``out`` or, if any ``return_*`` flag is set, the reference's 5-tuple
     ``(out, log_normalizer|None, total_attention|None, seed|None, offset|None)``
     (flash.py:160-169)."""
-    need_L = return_log_normalizer or return_total_attention
-    c = _Call(q, k, v, causal, sm_scale, dropout_p, need_L=need_L, q_rows=q_rows, backend=backend,
-              philox=philox, rescale=True)
-    c.run("faws_attention")
-    tot = None
-    if return_total_attention:
-        tot = torch.empty((c.B, c.H, c.N), device=c.dev, dtype=torch.float32)
-        c.run("faws_total_attention", C.c_void_p(tot.data_ptr()))
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if needs_grad:
+        if q_rows is not None:
+            raise ValueError("q_rows (a window of query rows) is not differentiable; pass the whole problem")
+        out, L, tot, seed, offset = _AttentionFunction.apply(q, k, v, causal, sm_scale, dropout_p,
+                                                             return_total_attention, backend, philox, kv_splits)
+    else:
+        need_L = return_log_normalizer or return_total_attention
+        c, tot = _attention_forward(q, k, v, causal, sm_scale, dropout_p, need_L, return_total_attention,
+                                    q_rows, backend, philox, kv_splits)
+        out, L, seed, offset = c.out, c.L, c.seed, c.offset
     if return_log_normalizer or return_total_attention or return_seed_offset:
-        return (c.out, c.L if return_log_normalizer else None, tot,
-                c.seed if return_seed_offset else None, c.offset if return_seed_offset else None)
-    return c.out
+        return (out, L if return_log_normalizer else None, tot,
+                seed if return_seed_offset else None, offset if return_seed_offset else None)
+    return out
 
 
 def attention_with_scores(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
@@ -173,6 +225,24 @@ def attention_with_scores(q, k, v, causal=False, sm_scale=None, dropout_p=0.0,
     sd = _lib.SCORES_F32 if scores_dtype == torch.float32 else _lib.SCORES_INPUT
     c.run("faws_attention_with_scores", C.c_void_p(scores.data_ptr()), sd, _f32_bits(masked_value))
     return c.out, scores
+
+
+def compute_attention_scores(q, k, causal=False, sm_scale=None, *, scores_dtype=None, backend=None):
+    """``q @ k^T * sm_scale`` as a (B,Hq,M,N) tensor in q.dtype, no softmax, no V: the reference's
+    ``compute_attention_scores`` (attention_scores.py:154-223).  ``causal`` is accepted and ignored,
+    exactly as there (:166,:171): no mask is applied.  ``scores_dtype=torch.float32`` keeps fp32."""
+    Dq, Dk = q.shape[-1], k.shape[-1]
+    assert Dq == Dk, "Q and K must have the same head_dim"
+    assert Dk in {16, 32, 64, 128}, f"head_dim must be one of 16, 32, 64, 128, got {Dk}"
+    assert q.shape[1] % k.shape[1] == 0, "num_heads_q must be a multiple of num_heads_k (GQA support)"
+    c = _Call(q, k, k, False, sm_scale, 0.0, out=q, backend=backend)
+    scores_dtype = q.dtype if scores_dtype is None else scores_dtype
+    if scores_dtype not in (torch.float32, q.dtype):
+        raise TypeError("scores_dtype must be torch.float32 or q.dtype")
+    scores = torch.empty((c.B, c.H, c.M, c.N), device=c.dev, dtype=scores_dtype)
+    sd = _lib.SCORES_F32 if scores_dtype == torch.float32 else _lib.SCORES_INPUT
+    c.run("faws_compute_attention_scores", C.c_void_p(scores.data_ptr()), sd)
+    return scores
 
 
 def attention_with_row_sum(q, k, v, causal=False, sm_scale=None, dropout_p=0.0, *, q_rows=None, backend=None,

@@ -17,7 +17,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OBJDIR = os.path.join(ROOT, "build", "libfaws")
 LIB = os.path.join(HERE, "libfaws.so")
-SOURCES = ["faws_abi.cu", "faws_generic.cu", "faws_tc.cu", "faws_noalloc.cu"]
+SOURCES = ["faws_abi.cu", "faws_generic.cu", "faws_tc.cu", "faws_tc_scores.cu", "faws_bwd.cu", "faws_tc_bwd.cu", "faws_noalloc.cu"]
 HEADERS = ["faws_internal.cuh", "faws_tc_ptx.cuh", "faws_tc_host.cuh"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -230,6 +230,38 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   return run_colsoftmax(p, c, sum_out, w.per_head, per_q_head ? 0 : 1, s);
 }
 
+// Number of key ranges for a problem that leaves most SMs idle: the plan of the reference's
+// num_splits_herustic (split_kv.py:234-262; its tiles are 16 x 128, here 128 x 128), i.e. the
+// smallest count whose wave efficiency is within 85 % of the best, among counts that leave no range
+// empty.
+int plan_splits(const faws_problem* p, int sms) {
+  const long long ctas = (long long)p->B * p->Hq * cdiv(p->M, kTcBlockM);
+  if (ctas * 10 >= 8LL * sms) return 1;
+  const int nkt = cdiv(p->N, kTcBlockN);
+  int max_splits = sms < nkt ? sms : nkt;
+  if (max_splits > 128) max_splits = 128;
+  if ((long long)p->B * max_splits > 65535) max_splits = 65535 / p->B;
+  double best = 0.0;
+  double eff[129];
+  for (int s = 1; s <= max_splits; ++s) {
+    const int per = cdiv(nkt, s);
+    eff[s] = -1.0;
+    if (s > 1 && per * s - nkt >= per) continue;  // the last range would be empty
+    const double waves = (double)(ctas * s) / sms;
+    const double whole = waves > (double)(long long)waves ? (double)((long long)waves + 1) : waves;
+    eff[s] = waves / whole;
+    if (eff[s] > best) best = eff[s];
+  }
+  for (int s = 1; s <= max_splits; ++s)
+    if (eff[s] >= 0.85 * best) return s;
+  return 1;
+}
+
+size_t split_kv_bytes(const faws_problem* p, int n_splits) {
+  return align256((size_t)p->B * p->Hq * n_splits * p->M * 4) +
+         align256((size_t)p->B * p->Hq * n_splits * p->M * p->D * 2);
+}
+
 }  // namespace
 }  // namespace faws
 
@@ -257,6 +289,74 @@ int faws_attention_with_scores(const faws_problem* p, void* scores, int32_t scor
   f.masked_bits = masked_bits;
   int bm, bn;
   return run_fwd(p, f, static_cast<cudaStream_t>(stream), &bm, &bn);
+}
+
+int32_t faws_split_kv_plan(const faws_problem* p) {
+  if (validate(p) != FAWS_OK) return 1;
+  if (p->dropout_p > 0.f || p->m_begin != 0 || p->m_end != p->M || p->backend == FAWS_BACKEND_GENERIC) return 1;
+  if (p->v.ptr == nullptr || p->out.ptr == nullptr) return 1;
+  FwdParams f = make_fwd(p);
+  if (!tc_fwd_supported(f, p->dtype)) return 1;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return plan_splits(p, sms);
+}
+
+int faws_attention_split_kv(const faws_problem* p, int32_t n_splits, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  const int nkt = cdiv(p->N, kTcBlockN);
+  if (n_splits < 1 || n_splits > nkt || (long long)p->B * n_splits > 65535) return FAWS_EINVAL;
+  if (p->dropout_p > 0.f) return FAWS_EUNSUPPORTED;  // the reference refuses dropout with split-KV too (flash.py:98)
+  if (p->m_begin != 0 || p->m_end != p->M) return FAWS_EINVAL;
+  if (n_splits == 1) return faws_attention(p, stream);
+  if (workspace == nullptr || workspace_bytes < split_kv_bytes(p, n_splits)) return FAWS_EWORKSPACE;
+  if (p->out.ptr == nullptr || p->v.ptr == nullptr) return FAWS_EINVAL;
+  FwdParams f = make_fwd(p);
+  if (p->backend == FAWS_BACKEND_GENERIC || !tc_fwd_supported(f, p->dtype)) return FAWS_EBACKEND;
+  float* L_part = static_cast<float*>(workspace);
+  char* o_part = static_cast<char*>(workspace) + align256((size_t)p->B * p->Hq * n_splits * p->M * 4);
+  f.o = o_part;
+  f.o_ss = p->D;
+  f.o_sh = (int64_t)p->M * p->D;  // per (query head, key range)
+  f.o_sb = (int64_t)p->Hq * n_splits * p->M * p->D;
+  f.L = L_part;
+  f.n_splits = n_splits;
+  f.tiles_per_split = cdiv(nkt, n_splits);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (launch_tc_fwd(f, p->dtype, s) != cudaSuccess) return FAWS_ECUDA;
+  if (launch_combine_splits(o_part, L_part, p->out.ptr, p->out.stride_b, p->out.stride_h, p->out.stride_s,
+                            p->log_normalizer, p->B, p->Hq, p->M, p->D, n_splits, p->dtype, s) != cudaSuccess)
+    return FAWS_ECUDA;
+  t_last_backend = FAWS_BACKEND_TCGEN05;
+  return FAWS_OK;
+}
+
+int faws_compute_attention_scores(const faws_problem* p, void* scores, int32_t scores_dtype, void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (scores == nullptr) return FAWS_EINVAL;
+  if (scores_dtype != FAWS_SCORES_F32 && scores_dtype != FAWS_SCORES_INPUT) return FAWS_EINVAL;
+  ScoresOnlyParams sp{};
+  sp.q = p->q.ptr; sp.k = p->k.ptr;
+  sp.q_sb = p->q.stride_b; sp.q_sh = p->q.stride_h; sp.q_ss = p->q.stride_s;
+  sp.k_sb = p->k.stride_b; sp.k_sh = p->k.stride_h; sp.k_ss = p->k.stride_s;
+  sp.scores = scores;
+  sp.scores_f32 = scores_dtype == FAWS_SCORES_F32 ? 1 : 0;
+  sp.B = p->B; sp.Hq = p->Hq; sp.Hk = p->Hk; sp.M = p->M; sp.N = p->N; sp.D = p->D;
+  sp.sm_scale = p->sm_scale;
+  bool use_tc = false;
+  if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_scores_only_supported(sp, p->dtype);
+  if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const cudaError_t e = use_tc ? launch_tc_scores_only(sp, p->dtype, s) : launch_generic_scores_only(sp, p->dtype, s);
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "faws: score-only launch failed: %s\n", cudaGetErrorString(e));
+    return FAWS_ECUDA;
+  }
+  t_last_backend = use_tc ? FAWS_BACKEND_TCGEN05 : FAWS_BACKEND_GENERIC;
+  return FAWS_OK;
 }
 
 int faws_attention_with_row_sum(const faws_problem* p, float* row_sum, void* stream) {
@@ -322,9 +422,54 @@ int faws_total_attention(const faws_problem* p, float* total, void* stream) {
   return run_colsoftmax(p, c, total, nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
+int faws_attention_backward(const faws_problem* p, const faws_grads* g, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  int st = validate(p);
+  if (st != FAWS_OK) return st;
+  if (g == nullptr || p->v.ptr == nullptr || p->out.ptr == nullptr || p->log_normalizer == nullptr ||
+      g->dout.ptr == nullptr || g->dq.ptr == nullptr || g->dk.ptr == nullptr || g->dv.ptr == nullptr)
+    return FAWS_EINVAL;
+  if (p->m_begin != 0 || p->m_end != p->M) return FAWS_EINVAL;
+  const size_t need = faws_workspace_bytes(FAWS_OP_ATTENTION_BACKWARD, p, 0);
+  if (workspace == nullptr || workspace_bytes < need) return FAWS_EWORKSPACE;
+  BwdParams b{};
+  b.q = p->q.ptr; b.k = p->k.ptr; b.v = p->v.ptr; b.o = p->out.ptr;
+  b.dout = g->dout.ptr; b.dq = g->dq.ptr; b.dk = g->dk.ptr; b.dv = g->dv.ptr;
+  b.q_sb = p->q.stride_b; b.q_sh = p->q.stride_h; b.q_ss = p->q.stride_s;
+  b.k_sb = p->k.stride_b; b.k_sh = p->k.stride_h; b.k_ss = p->k.stride_s;
+  b.v_sb = p->v.stride_b; b.v_sh = p->v.stride_h; b.v_ss = p->v.stride_s;
+  b.o_sb = p->out.stride_b; b.o_sh = p->out.stride_h; b.o_ss = p->out.stride_s;
+  b.do_sb = g->dout.stride_b; b.do_sh = g->dout.stride_h; b.do_ss = g->dout.stride_s;
+  b.dq_sb = g->dq.stride_b; b.dq_sh = g->dq.stride_h; b.dq_ss = g->dq.stride_s;
+  b.dk_sb = g->dk.stride_b; b.dk_sh = g->dk.stride_h; b.dk_ss = g->dk.stride_s;
+  b.dv_sb = g->dv.stride_b; b.dv_sh = g->dv.stride_h; b.dv_ss = g->dv.stride_s;
+  b.L = p->log_normalizer;
+  b.delta = static_cast<float*>(workspace);
+  b.B = p->B; b.Hq = p->Hq; b.Hk = p->Hk; b.G = p->Hq / p->Hk; b.M = p->M; b.N = p->N; b.D = p->D;
+  b.p_seq = p->N - p->M; b.causal = p->causal ? 1 : 0; b.sm_scale = p->sm_scale;
+  b.drop = make_drop(p);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (launch_bwd_delta(b, p->dtype, s) != cudaSuccess) return FAWS_ECUDA;
+  bool use_tc = false;
+  if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_bwd_supported(b, p->dtype);
+  if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
+  const cudaError_t e = use_tc ? launch_tc_bwd(b, p->dtype, s) : launch_generic_bwd(b, p->dtype, s);
+  if (e != cudaSuccess) {
+    std::fprintf(stderr, "faws: backward launch failed: %s\n", cudaGetErrorString(e));
+    return FAWS_ECUDA;
+  }
+  t_last_backend = use_tc ? FAWS_BACKEND_TCGEN05 : FAWS_BACKEND_GENERIC;
+  return FAWS_OK;
+}
+
 size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split) {
   if (validate(p) != FAWS_OK) return 0;
   switch (op) {
+    case FAWS_OP_ATTENTION_SPLIT_KV:  // `split` carries the number of key ranges
+      if (split < 1 || split > cdiv(p->N, kTcBlockN)) return 0;
+      return split == 1 ? 0 : split_kv_bytes(p, split);
+    case FAWS_OP_ATTENTION_BACKWARD:
+      return align256((size_t)p->B * p->Hq * p->M * 4);
     case FAWS_OP_COL_SUM:
     case FAWS_OP_COL_SUM_SEQUENTIAL:
       return align256(partial_floats(p, 0, p->N) * 4) + align256(qsum_floats(p) * 4);

@@ -278,6 +278,41 @@ __global__ void __launch_bounds__(NT) generic_fwd_kernel(FwdParams p, int vec) {
   }
 }
 
+// Score-only operator: one CTA writes a 64 x 64 tile of q.k^T * sm_scale (attention_scores.py:56-151).
+template <typename T>
+__global__ void __launch_bounds__(NT) generic_scores_only_kernel(ScoresOnlyParams p, int vec) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D = p.D, lds = D + 8;
+  T* Qs = reinterpret_cast<T*>(smem_raw);
+  T* Ks = Qs + BM * lds;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int n_nt = (p.N + BN - 1) / BN;
+  const int m0 = (blockIdx.x / n_nt) * BM, n0 = (blockIdx.x % n_nt) * BN;
+  const int h = blockIdx.y, b = blockIdx.z, hk = h / (p.Hq / p.Hk);
+  const T* qp = reinterpret_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+  const T* kp = reinterpret_cast<const T*>(p.k) + b * p.k_sb + hk * p.k_sh;
+  load_tile(Qs, lds, qp, p.q_ss, m0, 0, p.M, D, vec);
+  load_tile(Ks, lds, kp, p.k_ss, n0, 0, p.N, D, vec);
+  __syncthreads();
+  float acc[4][4];
+  tile_dot(Qs, Ks, lds, D, ty, tx, acc);
+  const int64_t bh = (int64_t)b * p.Hq + h;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int i = m0 + ty * 4 + r;
+    if (i >= p.M) continue;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int j = n0 + tx + 16 * c;
+      if (j >= p.N) continue;
+      const int64_t off = (bh * p.M + i) * (int64_t)p.N + j;
+      const float val = acc[r][c] * p.sm_scale;
+      if (p.scores_f32) reinterpret_cast<float*>(p.scores)[off] = val;
+      else reinterpret_cast<T*>(p.scores)[off] = from_f<T>(val);
+    }
+  }
+}
+
 // Key-major softmax column sums (the structure of total.py:50-142): a CTA owns
 // 64 keys and walks the query tiles; thread c < 64 accumulates column c in a
 // register in a fixed order, so there are no atomics and no partials.
@@ -551,6 +586,41 @@ __global__ void reduce_ranks_kernel(const float* parts, int n_ranks, int64_t cou
   out[i] = sum;
 }
 
+// Split-KV combine (the role of _fwd_combine_kv_splits, split_kv.py:163-227): every key range s left
+// a normalised partial result o_s and its log-normaliser L_s; out = sum_s exp(L_s - L) o_s with
+// L = log sum_s exp(L_s), added in the order s = 0, 1, ...  One warp per query row.
+template <typename T>
+__global__ void combine_splits_kernel(const T* __restrict__ o_part, const float* __restrict__ L_part, T* out,
+                                      int64_t o_sb, int64_t o_sh, int64_t o_ss, float* L, int B, int Hq, int M, int D,
+                                      int S) {
+  const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= (int64_t)B * Hq * M) return;
+  const int i = (int)(row % M);
+  const int64_t bh = row / M;
+  const int h = (int)(bh % Hq), b = (int)(bh / Hq);
+  const float* Ls = L_part + bh * S * M + i;
+  float mx = FAWS_NEG_INF;
+  for (int s = 0; s < S; ++s) mx = fmaxf(mx, Ls[(int64_t)s * M]);
+  float den = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const float l = Ls[(int64_t)s * M];
+    den += (l == FAWS_NEG_INF) ? 0.f : exp2f((l - mx) * kLog2e);
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  T* orow = out + b * o_sb + h * o_sh + (int64_t)i * o_ss;
+  for (int d = lane; d < D; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      const float l = Ls[(int64_t)s * M];
+      if (l == FAWS_NEG_INF) continue;
+      acc += exp2f((l - mx) * kLog2e) * to_f(o_part[((bh * S + s) * M + i) * (int64_t)D + d]);
+    }
+    orow[d] = from_f<T>(acc * inv);
+  }
+  if (L != nullptr && lane == 0) L[row] = den > 0.f ? mx + logf(den) : FAWS_NEG_INF;
+}
+
 size_t fwd_smem(int D) { return (size_t)(3 * 64 * (D + 8)) * 2 + (size_t)(BM * SLD + 3 * BM) * 4; }
 size_t cs_smem(int D) { return (size_t)(2 * 64 * (D + 8)) * 2 + (size_t)(BM * SLD + BM) * 4; }
 
@@ -580,6 +650,18 @@ cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
     if ((e = set_smem(generic_fwd_kernel<__nv_bfloat16>, smem)) != cudaSuccess) return e;
     generic_fwd_kernel<__nv_bfloat16><<<grid, NT, smem, s>>>(p, vec);
   }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_generic_scores_only(const ScoresOnlyParams& p, int dtype, cudaStream_t s) {
+  const int vec = aligned16(p.q, p.q_sb, p.q_sh, p.q_ss) && aligned16(p.k, p.k_sb, p.k_sh, p.k_ss);
+  const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  if (tiles <= 0 || tiles > 0x7fffffffLL) return tiles <= 0 ? cudaSuccess : cudaErrorInvalidValue;
+  dim3 grid((unsigned)tiles, p.Hq, p.B);
+  const size_t smem = (size_t)(2 * 64 * (p.D + 8)) * 2;
+  if (dtype == FAWS_FP16) generic_scores_only_kernel<__half><<<grid, NT, smem, s>>>(p, vec);
+  else generic_scores_only_kernel<__nv_bfloat16><<<grid, NT, smem, s>>>(p, vec);
   count_launch();
   return cudaGetLastError();
 }
@@ -631,6 +713,23 @@ cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, 
   if (len <= 0) return cudaSuccess;
   dim3 grid((len + 255) / 256, Hk, B);
   group_sum_kernel<<<grid, 256, 0, s>>>(in, out, Hk, G, len);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_splits(const void* o_part, const float* L_part, void* out, int64_t o_sb, int64_t o_sh,
+                                  int64_t o_ss, float* L, int B, int Hq, int M, int D, int n_splits, int dtype,
+                                  cudaStream_t s) {
+  const int64_t rows = (int64_t)B * Hq * M;
+  const unsigned blocks = (unsigned)((rows * 32 + 255) / 256);
+  if (dtype == FAWS_FP16)
+    combine_splits_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(o_part), L_part,
+                                                         static_cast<__half*>(out), o_sb, o_sh, o_ss, L, B, Hq, M, D,
+                                                         n_splits);
+  else
+    combine_splits_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(o_part), L_part,
+                                                                static_cast<__nv_bfloat16*>(out), o_sb, o_sh, o_ss, L,
+                                                                B, Hq, M, D, n_splits);
   count_launch();
   return cudaGetLastError();
 }

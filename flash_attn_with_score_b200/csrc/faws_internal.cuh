@@ -79,7 +79,9 @@ struct FwdParams {
   int split;
   int lpt_order;         // set by the tcgen05 launcher: heaviest causal row blocks of all heads first
   int fill_ctas;         // set by the tcgen05 launcher: masked score tiles are written by extra CTAs
-  int pair_tiles;        // set by the tcgen05 launcher: a CTA owns query tiles c and n_tiles-1-c (causal balance)
+  int n_splits;          // split-KV: key ranges per (batch, head); 0 or 1 = off.  o and L then address the
+                         // partial buffers (B, Hq*n_splits, M, D) and (B, Hq, n_splits, M)
+  int tiles_per_split;   // key tiles per range
   int col_lin;           // column hook skips tiles that col_tile_linear() accepts (see below)
   int col_row_lo;        // max(col_row_begin, m_begin): first query row that contributes
   float* qsum;           // col_lin: (B,Hq,ceil(M/128),128) per-tile sums of the query rows, written by the
@@ -135,7 +137,50 @@ struct ReducePartialParams {
   float sm_scale;
 };
 
+// Backward pass of attention(): inputs q, k, v, out, dout, L; outputs dq (B,Hq,M,D), dk, dv (B,Hk,N,D).
+struct BwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* dout;
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  int64_t v_sb, v_sh, v_ss;
+  int64_t o_sb, o_sh, o_ss;
+  int64_t do_sb, do_sh, do_ss;
+  int64_t dq_sb, dq_sh, dq_ss;
+  int64_t dk_sb, dk_sh, dk_ss;
+  int64_t dv_sb, dv_sh, dv_ss;
+  const float* L;  // (B,Hq,M) log-normaliser saved by the forward pass
+  float* delta;    // (B,Hq,M) scratch: sum_d out * dout per query row
+  int B, Hq, Hk, G, M, N, D;
+  int p_seq, causal;
+  float sm_scale;
+  DropoutParams drop;  // out_scale unused: the kept weights are rescaled by 1/(1-p) (flash.py:655,713,724)
+};
+
+// Score-only operator (compute_attention_scores, attention_scores.py:154-223): scores = q.k^T * sm_scale.
+struct ScoresOnlyParams {
+  const void* q;
+  const void* k;
+  int64_t q_sb, q_sh, q_ss;
+  int64_t k_sb, k_sh, k_ss;
+  void* scores;    // (B,Hq,M,N) contiguous
+  int scores_f32;  // 1: fp32, 0: the dtype of q
+  int B, Hq, Hk, M, N, D;
+  float sm_scale;
+};
+
 // Launchers (each returns a cudaError_t from the launch).
+cudaError_t launch_generic_scores_only(const ScoresOnlyParams& p, int dtype, cudaStream_t s);
+bool tc_scores_only_supported(const ScoresOnlyParams& p, int dtype);
+cudaError_t launch_tc_scores_only(const ScoresOnlyParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_bwd_delta(const BwdParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_generic_bwd(const BwdParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_generic_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_generic_colsoftmax(const ColSoftmaxParams& p, int dtype, cudaStream_t s);
 cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cudaStream_t s);
@@ -144,6 +189,11 @@ cudaError_t launch_group_sum(const float* in, float* out, int B, int Hk, int G, 
                              cudaStream_t s);
 cudaError_t launch_reduce_ranks(const float* parts, int n_ranks, int64_t count, float* out,
                                 cudaStream_t s);
+// out (B,Hq,M,D) and L (B,Hq,M) or null from the split-KV partials o_part (B,Hq,S,M,D) in the dtype of q
+// and L_part (B,Hq,S,M)
+cudaError_t launch_combine_splits(const void* o_part, const float* L_part, void* out, int64_t o_sb, int64_t o_sh,
+                                  int64_t o_ss, float* L, int B, int Hq, int M, int D, int n_splits, int dtype,
+                                  cudaStream_t s);
 
 // tcgen05 family.  tc_supported() is a pure host-side check.
 bool tc_fwd_supported(const FwdParams& p, int dtype);
@@ -151,6 +201,9 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s);
 bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype);
 bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p);
 cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, int group_sum, cudaStream_t s);
+
+bool tc_bwd_supported(const BwdParams& p, int dtype);
+cudaError_t launch_tc_bwd(const BwdParams& p, int dtype, cudaStream_t s);
 
 int tc_read_status(int reset);  // synchronising read of the device status word
 cudaError_t launch_wait_give_up(cudaStream_t s);  // self-test: a bounded wait that runs out

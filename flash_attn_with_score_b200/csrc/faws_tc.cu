@@ -161,33 +161,24 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   // CTA and a fill CTA that only writes the row block's never-visited key tiles; interleaved so
   // that their costs decrease together (heaviest compute block, most-masked fill block, ...).
   const int slot = (int)(p.lpt_order ? blockIdx.z : blockIdx.x);
-  const int nslots = (int)(p.lpt_order ? gridDim.z : gridDim.x);
-  const int ncb = nslots >> (p.fill_ctas ? 1 : 0);
-  // pair_tiles: all compute CTAs come first in launch order, the fill CTAs after them
-  const bool is_fill = p.fill_ctas && (p.pair_tiles ? slot >= ncb : (slot & 1));
-  const int cb_slot = !p.fill_ctas ? slot : (p.pair_tiles ? (is_fill ? slot - ncb : slot) : (slot >> 1));
-  const int cb_rel = (is_fill || p.pair_tiles) ? cb_slot : ncb - 1 - cb_slot;  // heaviest (last) blocks first
+  const int ncb = (int)(p.lpt_order ? gridDim.z : gridDim.x) >> (p.fill_ctas ? 1 : 0);
+  const bool is_fill = p.fill_ctas && (slot & 1);
+  const int cb_slot = p.fill_ctas ? (slot >> 1) : slot;
+  const int cb_rel = is_fill ? cb_slot : ncb - 1 - cb_slot;  // heaviest (last) blocks first
   const int h = p.lpt_order ? blockIdx.x : blockIdx.y;
-  const int b = p.lpt_order ? blockIdx.y : blockIdx.z;
+  // Split-KV launches (n_splits > 1) fold the key-range index into the batch axis of the grid.
+  const int bz = p.lpt_order ? blockIdx.y : blockIdx.z;
+  const int b = bz / p.n_splits;
+  const int ksplit = bz - b * p.n_splits;
+  const int kt0 = ksplit * p.tiles_per_split;  // this CTA visits key tiles [kt0, kt0 + tiles_per_split)
   const int hk = h / p.G;
   const int bh = b * p.Hq + h;
+  const int ho = h * p.n_splits + ksplit;  // head index of the (partial) output this CTA writes
 
-  // First row of the CTA's query tile(s).  Default: two adjacent tiles.  pair_tiles (causal): tile
-  // c from the top of the window together with tile c from its bottom, so that every CTA of the
-  // launch visits the same number of (query tile, key tile) pairs; a tile index past the middle
-  // is parked on the first row beyond the window (no rows, no key tiles).
+  // first row of the CTA's query tile(s)
   int r_tile_of[2];
-  if (SPLIT) {
-    r_tile_of[0] = r_tile_of[1] = p.m_begin + cb_rel * BM;
-  } else if (p.pair_tiles) {
-    const int n_tiles = (p.m_end - p.m_begin + BM - 1) / BM;
-    const int hi_tile = n_tiles - 1 - cb_rel;
-    r_tile_of[0] = p.m_begin + cb_rel * BM;
-    r_tile_of[1] = p.m_begin + (hi_tile > cb_rel ? hi_tile : n_tiles) * BM;
-  } else {
-    r_tile_of[0] = p.m_begin + cb_rel * CTA_ROWS;
-    r_tile_of[1] = r_tile_of[0] + BM;
-  }
+  r_tile_of[0] = p.m_begin + cb_rel * CTA_ROWS;
+  r_tile_of[1] = r_tile_of[0] + (SPLIT ? 0 : BM);
   const int cb_abs = r_tile_of[0] / CTA_ROWS;  // start offset of the round-robin key-tile order
 
   // key tiles each query tile visits (0 for a tile that lies outside the row window)
@@ -200,9 +191,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       hi = p.N;
       if (p.causal) hi = max(0, min(p.N, p.p_seq + min(r0 + BM, p.m_end)));
     }
-    nt_q[t] = (hi + BN - 1) / BN;
+    nt_q[t] = min(max((hi + BN - 1) / BN, kt0), kt0 + p.tiles_per_split);  // end of the tile's key-tile range
   }
-  const int nt = max(nt_q[0], nt_q[1]);
+  const int nt = max(nt_q[0], nt_q[1]) - kt0;  // key tiles this CTA visits
 
   if constexpr (HOOK == kHookScores || HOOK == kHookScores16) {
     if (is_fill) {
@@ -242,9 +233,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   }
 
   auto tile_of = [&](int it) -> int {
-    if (p.schedule == kReverse) return nt - 1 - it;
-    if (p.schedule == kRoundRobin) return (cb_abs + it) % nt;
-    return it;
+    if (p.schedule == kReverse) return kt0 + nt - 1 - it;
+    if (p.schedule == kRoundRobin) return kt0 + (cb_abs + it) % nt;
+    return kt0 + it;
   };
   // K(0), V(0), K(1), V(1), ... go through the ring in this order
   auto issue_kv_load = [&](int idx) {
@@ -794,7 +785,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     const float rs = rs_raw * scale;
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
-    if (alive && my_nt > 0) {
+    if (alive && my_nt > kt0) {
       if (!mbar_wait(&bars->o_done, 0, abort_flag)) alive = false;
       tc_fence_after();
     }
@@ -825,7 +816,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     if (write_out) {
       float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       if constexpr (DROP) inv *= p.drop.out_scale;
-      if (my_nt > 0) {
+      if (my_nt > kt0) {
         // Every MMA of the CTA has completed, so the Q tiles' shared memory is free: each warp
         // stages its 32 x D output block there (128B-swizzled) and stores it with TMA.
         unsigned char* ost = smem + L::q_off + (warp - 4) * (32 * D * 2);
@@ -869,19 +860,19 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         __syncwarp();
         if (lane == 0) {
           for (int sub = 0; sub < D / 64; ++sub)
-            tma_store_4d(&maps.o, ost + sub * 4096, sub * 64, r_tile + lg * 32 - p.m_begin, h, b);
+            tma_store_4d(&maps.o, ost + sub * 4096, sub * 64, r_tile + lg * 32 - p.m_begin, ho, b);
           tma_store_commit();
         }
       } else if (row_ok) {
         // no key is visible to this query tile: its rows are zero
-        T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + h * p.o_sh + (int64_t)i * p.o_ss;
+        T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + ho * p.o_sh + (int64_t)i * p.o_ss;
         const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
         for (int g = 0; g < D / 8; ++g) *reinterpret_cast<uint4*>(orow + g * 8) = z;
       }
       if (row_ok) {
         if (p.L != nullptr)
-          p.L[(int64_t)bh * p.M + i] = l_all > 0.f ? (m_all + log2f(l_all)) * kLn2 : FAWS_NEG_INF;
+          p.L[((int64_t)bh * p.n_splits + ksplit) * p.M + i] = l_all > 0.f ? (m_all + log2f(l_all)) * kLn2 : FAWS_NEG_INF;
         if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs_all;
       }
     }
@@ -1202,22 +1193,10 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   pp.lpt_order = (p.causal && kv_bytes <= (48LL << 20) && 2 * ncb <= 65535) ? 1 : 0;
   // masked key tiles exist (causal, some row block ends before N): give them their own CTAs
   pp.fill_ctas = ((HOOK == kHookScores || HOOK == kHookScores16) && p.causal && p.p_seq + p.m_begin + 128 < p.N) ? 1 : 0;
-  // Causal launches whose CTAs all fit on the GPU at once, or fill whole waves: pair light and heavy
-  // query tiles so that every CTA has the same length.  With uneven last waves the heaviest-first
-  // order of unequal CTAs packs better.
-  if (!SPLIT && p.causal && ncb >= 2) {
-    const long long ctas = (long long)ncb * p.Hq * p.B;
-    const int sms = sm_count();
-    const long long waves = (ctas + sms - 1) / sms;
-    pp.pair_tiles = (ctas <= sms || (double)(waves * sms) / (double)ctas <= 1.03) ? 1 : 0;
-    static const int forced_pair = [] {  // FAWS_PAIR_TILES=0/1 overrides the choice (tests)
-      const char* e = std::getenv("FAWS_PAIR_TILES");
-      return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
-    }();
-    if (forced_pair >= 0) pp.pair_tiles = forced_pair;
-  }
   const int nslots = pp.fill_ctas ? 2 * ncb : ncb;
-  dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B, nslots) : dim3(nslots, p.Hq, p.B);
+  if (pp.n_splits < 1) pp.n_splits = 1;
+  if (pp.n_splits == 1) pp.tiles_per_split = (p.N + BN - 1) / BN;
+  dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B * pp.n_splits, nslots) : dim3(nslots, p.Hq, p.B * pp.n_splits);
   // Programmatic stream serialization: this launch may begin (CTA placement, barrier and TMEM set-up)
   // while the previous kernel of the stream drains; the kernel waits before any global access.
   cudaLaunchConfig_t cfg{};
@@ -1306,7 +1285,9 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
       !make_map_bhsd(&maps.v, p.v, p.D, p.N, p.Hk, p.B, p.v_ss, p.v_sh, p.v_sb, 128))
     return cudaErrorInvalidValue;
   const char* obase = static_cast<const char*>(p.o) + (int64_t)p.m_begin * p.o_ss * 2;
-  if (!make_map_bhsd(&maps.o, obase, p.D, q_rows, p.Hq, p.B, p.o_ss, p.o_sh, p.o_sb, 32)) return cudaErrorInvalidValue;
+  // split-KV: p.o is the (B, Hq * n_splits, M, D) buffer of partial results
+  const int o_heads = p.Hq * (p.n_splits > 1 ? p.n_splits : 1);
+  if (!make_map_bhsd(&maps.o, obase, p.D, q_rows, o_heads, p.B, p.o_ss, p.o_sh, p.o_sb, 32)) return cudaErrorInvalidValue;
   maps.st = maps.q;
   if (p.scores != nullptr) {
     const int esize = p.scores_f32 ? 4 : 2;
@@ -1324,7 +1305,6 @@ cudaError_t launch_tc_fwd(const FwdParams& p, int dtype, cudaStream_t s) {
     return p.D == 128 ? launch_fwd_t<__half, 128>(maps, p, s) : launch_fwd_t<__half, 64>(maps, p, s);
   return p.D == 128 ? launch_fwd_t<__nv_bfloat16, 128>(maps, p, s) : launch_fwd_t<__nv_bfloat16, 64>(maps, p, s);
 }
-
 
 namespace {
 // Exercises the give-up path of mbar_wait: one thread waits (bounded, about a millisecond) on an

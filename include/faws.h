@@ -64,6 +64,8 @@ extern "C" {
 #define FAWS_OP_CROSS_SOFTMAX_SUM 7
 #define FAWS_OP_CROSS_SOFTMAX_SUM_BUFFERED 8
 #define FAWS_OP_TOTAL_ATTENTION 9
+#define FAWS_OP_ATTENTION_BACKWARD 10
+#define FAWS_OP_ATTENTION_SPLIT_KV 11
 
 /* A (B,H,S,D) view; strides in elements; the D axis has stride 1. */
 typedef struct faws_tensor {
@@ -126,6 +128,32 @@ int faws_attention(const faws_problem* p, void* stream);
  */
 int faws_attention_with_scores(const faws_problem* p, void* scores, int32_t scores_dtype,
                                uint32_t masked_bits, void* stream);
+
+/*
+ * Split-KV ("flash-decoding") form of faws_attention for problems with few query rows, where one
+ * CTA per (batch, head, 128 query rows) would leave most SMs idle: replaces the split path of
+ * FlashAttention.forward (flash.py:68-70,97-134; kernels split_kv.py:14-227).  The keys are cut
+ * into n_splits contiguous ranges of whole 128-key tiles, each range is attended to by its own
+ * CTAs, which leave a normalised partial result in the dtype of q and its log-normaliser in the
+ * workspace (the reference's multiple_o / multiple_l, flash.py:106-107), and a combine kernel
+ * merges the ranges in a fixed order (deterministic).  faws_split_kv_plan returns the number of
+ * ranges the library would choose for p (the rule of split_kv.py:234-262; 1 = do not split: enough
+ * CTAs already, dropout, a query-row window, or a problem the tcgen05 kernels cannot take).
+ * Workspace: faws_workspace_bytes(FAWS_OP_ATTENTION_SPLIT_KV, p, n_splits).  Dropout is refused
+ * (FAWS_EUNSUPPORTED), as in the reference (flash.py:98).
+ */
+int32_t faws_split_kv_plan(const faws_problem* p);
+int faws_attention_split_kv(const faws_problem* p, int32_t n_splits, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/*
+ * Replaces compute_attention_scores (attention_scores.py:154-223, kernel :56-151): the score
+ * tensor alone, scores = q.k^T * sm_scale, (B,Hq,M,N) contiguous in the dtype of q (what the
+ * reference writes, :203) or fp32.  No mask is applied whatever p->causal says: the reference
+ * accepts `causal` and ignores it (:166,:171,:195).  p->v, p->out and the query-row window are
+ * not used.
+ */
+int faws_compute_attention_scores(const faws_problem* p, void* scores, int32_t scores_dtype, void* stream);
 
 /* Replaces attention_with_row_sum (attention_with_row_sum.py:204-326).
  * row_sum: (B,Hq,M) fp32, sum over visible keys of q.k^T * sm_scale. */
@@ -217,6 +245,23 @@ int faws_attention_cross_token_softmax_sum_buffered(const faws_problem* p, int32
  * v and out are ignored.  total: (B,Hq,N) fp32.
  */
 int faws_total_attention(const faws_problem* p, float* total, void* stream);
+
+/*
+ * Replaces FlashAttention.backward (flash.py:172-261; kernels flash.py:532-577 delta pre-pass,
+ * :581-754 dK/dV, :758-918 dQ).  Inputs: p->q, p->k, p->v, p->out (the forward result),
+ * p->log_normalizer (the forward pass's L, required) and g->dout, the gradient of out.  Outputs:
+ * g->dq (B,Hq,M,D); g->dk, g->dv (B,Hk,N,D), already summed over the G query heads of each kv head
+ * (the reference sums per-query-head tensors on the host, flash.py:259-260).  All tensors in the
+ * dtype of q.  Dropout: pass the forward call's dropout_p and philox pair; dropout_scale is not
+ * used (kept weights are rescaled by 1/(1-p), flash.py:655,713,724).  The query-row window must
+ * be the whole problem.  Deterministic: no atomics.  Workspace:
+ * faws_workspace_bytes(FAWS_OP_ATTENTION_BACKWARD, p, 0).
+ */
+typedef struct faws_grads {
+  faws_tensor dout, dq, dk, dv;
+} faws_grads;
+int faws_attention_backward(const faws_problem* p, const faws_grads* g, void* workspace,
+                            size_t workspace_bytes, void* stream);
 
 /* Bytes of scratch `op` needs for `p` (0 if none).  Alignment: 256 bytes. */
 size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split);

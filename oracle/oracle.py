@@ -14,6 +14,8 @@ own PyTorch oracle and of the derivations its verifier applies to that oracle:
                                     verifier never checks this quantity
                                     (benchmark.py:1352 stores it, nothing reads it)
 * ``log_normalizer``                flash.py:486  (L = m*sm_scale + log(l))
+* ``attention_backward``            torch autograd through the formulas above: the gradients
+                                    FlashAttention.backward (flash.py:172-261) computes
 * ``group_sum``                     the (B,Hk,.) layout the reference kernels
                                     return because their output pointer is
                                     offset by the kv head (attention_with_col_sum.py:72)
@@ -229,6 +231,73 @@ def dropout_softmax_col_sum(scores, keep):
     out and nothing is rescaled (attention_with_col_softmax_sum.py:238-244)."""
     return (softmax_weights(scores) * keep.float()).sum(dim=-2)
 
+
+
+# -- backward pass ---------------------------------------------------------------
+def attention_backward(q, k, v, dout, causal, sm_scale=None, p_seq=0, keep=None, dropout_p=0.0):
+    """(dq, dk, dv) of out = softmax(mask(q k^T * sm_scale)) v with respect to fp32 copies of the
+    inputs, by torch autograd through the same formulas as naive_attention_with_scores (what
+    FlashAttention.backward, flash.py:172-261, computes).  dk, dv come out in the (B,Hk,N,D) layout:
+    autograd sums the G query heads of a kv head (flash.py:259-260).  ``keep`` (B,Hq,M,N) bool and
+    ``dropout_p`` apply the forward pass's dropout mask (weights kept are rescaled by 1/(1-p))."""
+    q = q.detach().float().requires_grad_(True)
+    k = k.detach().float().requires_grad_(True)
+    v = v.detach().float().requires_grad_(True)
+    B, Hq, M, D = q.shape
+    Hk, N = k.shape[1], k.shape[2]
+    g = Hq // Hk
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    scores = torch.matmul(q, _expand_kv(k, g).transpose(-2, -1)) * sm_scale
+    if causal:
+        scores = scores.masked_fill(causal_mask(M, N, p_seq), float("-inf"))
+    w = torch.nan_to_num(torch.softmax(scores, dim=-1), nan=0.0)
+    if keep is not None:
+        w = w * keep.float() * (1.0 / (1.0 - dropout_p))
+    out = torch.matmul(w, _expand_kv(v, g))
+    out.backward(dout.float())
+    return q.grad, k.grad, v.grad
+
+
+GRAD_ATOL = 2e-3
+
+
+def grad_slack(q, k, v, dout, causal, sm_scale=None, p_seq=0, bf16=False):
+    """Error a 16-bit pipeline cannot avoid in (dq, dk, dv), per element, from two roundings the
+    reference's kernels perform as well: ``out`` is stored in 16 bits before delta_i = sum_d
+    out_id * dout_id is taken from it (flash.py:202-213), which moves delta_i by at most
+    e_i = eps * sum_d |out_id * dout_id| and hence dq_i by sm_scale * e_i * sum_j p_ij |k_j| and dk_j
+    by sm_scale * sum_i p_ij e_i |q_i|; and P is rounded to 16 bits before P^T dO (flash.py:704),
+    which moves dv_j by at most eps * sum_i p_ij |dout_i|.  eps = 2^-11 (fp16) or 2^-8 (bf16)."""
+    eps = 2.0 ** -8 if bf16 else 2.0 ** -11
+    q, k, v, dout = q.float(), k.float(), v.float(), dout.float()
+    B, Hq, M, D = q.shape
+    Hk = k.shape[1]
+    g = Hq // Hk
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    out, scores = naive_attention_with_scores(q, k, v, causal, sm_scale, p_seq)
+    p = softmax_weights(scores)
+    e = eps * (out * dout).abs().sum(-1, keepdim=True)  # (B,Hq,M,1)
+    s_dq = sm_scale * e * torch.matmul(p, _expand_kv(k.abs(), g))
+    s_dk = sm_scale * torch.matmul(p.transpose(-2, -1), e * q.abs())
+    s_dv = eps * torch.matmul(p.transpose(-2, -1), dout.abs())
+    fold = lambda x: x.view(B, Hk, g, *x.shape[2:]).sum(2)  # noqa: E731
+    return s_dq, fold(s_dk), fold(s_dv)
+
+
+def check_grad(x, ref, bf16=False, slack=None):
+    """|x - ref| <= 2e-3 * max(1, rms(ref)) + rel * |ref| (+ ``slack`` from grad_slack); rel = 2^-10
+    (fp16 tensors) or 2^-7 (bf16): rounding of the stored 16-bit result."""
+    x = x.double()
+    ref = ref.double()
+    rms = ref.pow(2).mean().sqrt().item()
+    rel = 2.0 ** -7 if bf16 else 2.0 ** -10
+    tol = GRAD_ATOL * max(1.0, rms) + rel * ref.abs()
+    if slack is not None:
+        tol = tol + slack.double()
+    viol = (x - ref).abs() - tol
+    return bool((viol <= 0).all()), viol.max().item(), (x - ref).abs().max().item()
 
 
 # ---------------------------------------------------------------------------

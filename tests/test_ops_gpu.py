@@ -293,14 +293,11 @@ def test_query_split_two_gpus_nccl():
     mp.spawn(_query_split_worker, args=(2, port, q, k, v, 256, want_col, want_x), nprocs=2, join=True)
 
 
-@pytest.mark.parametrize("env", [{"FAWS_SPLIT_KV": "0", "FAWS_PAIR_TILES": "0"}, {"FAWS_SPLIT_KV": "1"},
-                                 {"FAWS_SPLIT_KV": "0", "FAWS_PAIR_TILES": "1"}],
-                         ids=["two_adjacent_query_tiles", "split_kv", "paired_query_tiles"])
+@pytest.mark.parametrize("env", [{"FAWS_SPLIT_KV": "0"}, {"FAWS_SPLIT_KV": "1"}], ids=["two_query_tiles", "split_kv"])
 def test_every_cta_mode_of_the_forward_kernel(env):
-    """The tcgen05 forward kernel has three CTA shapes: two adjacent query tiles per CTA; one query
-    tile whose key tiles are split over the two softmax warpgroups; and, for causal problems, a
-    light query tile paired with a heavy one.  The library picks by launch size; here each is forced
-    through FAWS_SPLIT_KV / FAWS_PAIR_TILES in a child process running the tcgen05 parity tests."""
+    """The tcgen05 forward kernel has two CTA shapes (two query tiles per CTA, or one query tile whose
+    key tiles are split over the two softmax warpgroups).  The library picks by launch size; here each
+    is forced through FAWS_SPLIT_KV in a child process running the tcgen05 parity tests."""
     import os
     import subprocess
     import sys
