@@ -163,9 +163,7 @@ class _AttentionFunction(torch.autograd.Function):
         ctx.save_for_backward(c.q, c.k, c.v, c.out, c.L)
         ctx.causal, ctx.sm_scale, ctx.dropout_p, ctx.backend = causal, float(c.p.sm_scale), dropout_p, backend
         ctx.philox = (c.seed, c.offset) if c.seed is not None else None
-        ctx.mark_non_differentiable(c.L)
-        if tot is not None:
-            ctx.mark_non_differentiable(tot)
+        ctx.mark_non_differentiable(*[t for t in (c.L, tot) if t is not None])
         return c.out, c.L, tot, c.seed, c.offset
 
     @staticmethod

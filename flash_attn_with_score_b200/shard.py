@@ -85,15 +85,35 @@ def all_reduce_rank_order(part: torch.Tensor, group=None) -> torch.Tensor:
     return sum_in_rank_order(gathered)
 
 
-def query_split(op, q, k, v, *args, group=None, **kwargs):
+def query_split(op, q, k, v, *args, group=None, overlap=False, **kwargs):
     """Run a column-type operator with this rank's window of query rows and reduce its sums.
 
     ``op`` is one of the package's column-type operators (col_sum, col_sum_sequential,
     softmax_col_sum, cross_token_*).  Every rank passes the same q, k, v.  Returns
     ``(out, sums, (begin, end))``: only rows [begin, end) of ``out`` are written on this rank;
-    ``sums`` is complete and identical on every rank."""
+    ``sums`` is complete and identical on every rank.
+
+    ``overlap=True`` walks the batch one element at a time and starts the all-gather of an element's
+    partial sums as soon as they exist, so the exchange of element b runs on NCCL's stream while
+    the kernels of element b + 1 compute; the rank-order reduce follows at the end.  Same bits."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     begin, end = plan_query_rows(q.shape[2], world)[rank]
-    out, part = op(q, k, v, *args, q_rows=(begin, end), **kwargs)
-    return out, all_reduce_rank_order(part, group), (begin, end)
+    if not overlap or world == 1 or q.shape[0] == 1:
+        out, part = op(q, k, v, *args, q_rows=(begin, end), **kwargs)
+        return out, all_reduce_rank_order(part, group), (begin, end)
+    B = q.shape[0]
+    out = torch.empty_like(q)
+    landing, handles = [], []
+    for b in range(B):
+        o_b, part = op(q[b:b + 1], k[b:b + 1], v[b:b + 1], *args, q_rows=(begin, end), **kwargs)
+        out[b:b + 1, :, begin:end] = o_b[:, :, begin:end]
+        part = part.contiguous()
+        flat = torch.empty((world * part.shape[0],) + tuple(part.shape[1:]), device=part.device, dtype=part.dtype)
+        handles.append(dist.all_gather_into_tensor(flat, part, group=group, async_op=True))
+        landing.append(flat.view((world,) + tuple(part.shape)))  # rank-major: the reduce kernel's input
+    sums = []
+    for h, gathered in zip(handles, landing):
+        h.wait()
+        sums.append(sum_in_rank_order(gathered))
+    return out, torch.cat(sums, 0), (begin, end)

@@ -63,6 +63,23 @@ def _worker(rank, world, port, fail_rank):
         b, e = shard.plan_query_rows(M, world)[rank]
         col = shard.all_reduce_rank_order(scores[b:e].sum(0))
         assert torch.allclose(col, scores.sum(0), atol=1e-4)
+        # query_split over a stand-in operator (column sums of the window's rows), both exchange forms
+        q = torch.randn(3, 2, 512, 8, generator=torch.Generator().manual_seed(11))
+        kk = torch.randn(3, 1, 40, 8, generator=torch.Generator().manual_seed(12))
+
+        def fake_op(q_, k_, v_, q_rows=None):
+            lo, hi = q_rows
+            sc = torch.einsum("bhmd,bknd->bhmn", q_, k_)
+            return q_.clone(), sc[:, :, lo:hi].sum(2)
+
+        want_sums = torch.einsum("bhmd,bknd->bhmn", q, kk)
+        lo0, hi0 = shard.plan_query_rows(512, world)[0]
+        want_sums = want_sums[:, :, lo0:hi0].sum(2) + want_sums[:, :, hi0:].sum(2)  # rank order, world 2
+        for overlap in (False, True):
+            out, sums, (lo, hi) = shard.query_split(fake_op, q, kk, kk, overlap=overlap)
+            assert (lo, hi) == shard.plan_query_rows(512, world)[rank]
+            assert torch.equal(sums, want_sums), overlap
+            assert torch.equal(out[:, :, lo:hi], q[:, :, lo:hi])
         if fail_rank == rank:
             raise RuntimeError("injected host-side failure before the next exchange")
         dist.barrier()
