@@ -268,42 +268,261 @@ def ops_table(F, device, pk):
                          "gbs": nbytes / (ms * 1e-3) / 1e9, "bound": bound,
                          "frac": max(t_tensor, t_hbm) / (ms * 1e-3), "backend": F.last_backend()})
         del q, k, v
+    rows += extra_rows(F, device, pk)
     return rows
 
 
-def query_split_leg(F, device, world, pk):
+def extra_rows(F, device, pk):
+    """Backward pass, score-only operator and split-KV decoding, same timing as the rows above."""
+    rows = []
+
+    def add(config, op, ms, flops, nbytes, note=None):
+        t_tensor, t_hbm = flops / (pk["tensor"] * 1e12), nbytes / (pk["hbm"] * 1e9)
+        r = {"config": config, "op": op, "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9,
+             "bound": "tensor" if t_tensor >= t_hbm else "hbm", "frac": max(t_tensor, t_hbm) / (ms * 1e-3),
+             "backend": F.last_backend()}
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    # backward of attention on cfg3: dq, dk, dv from (q, k, v, out, L, dout); 5 GEMMs per (query, key) tile pair
+    cfg3 = dict(B=1, Hq=28, Hk=4, S=4096, D=128, dtype=torch.bfloat16, causal=True, vscale=0.5)
+    q, k, v = (t.requires_grad_(True) for t in make_inputs(cfg3, 0, device))
+    out = F.attention(q, k, v, True)
+    do = torch.randn_like(out)
+    ms = time_op(lambda: torch.autograd.grad(out, (q, k, v), do, retain_graph=True), 10, 2)
+    pairs = cfg3["S"] * (cfg3["S"] + 1) // 2
+    io = (3 * cfg3["Hq"] + 4 * cfg3["Hk"]) * cfg3["S"] * cfg3["D"] * 2 + cfg3["Hq"] * cfg3["S"] * cfg3["D"] * 2
+    add("cfg3", "attention_backward", ms, cfg3["Hq"] * cfg3["D"] * 10 * pairs, io,
+        "algorithmic work = 5 GEMMs per tile pair; the two-kernel form computes 7 (q.k^T and dout.v^T twice)")
+    del q, k, v, out, do
+
+    # score-only operator on cfg2's shape, fp16 scores (the reference's output format)
+    q, k, _ = make_inputs(CFG2, 0, device)
+    ms = time_op(lambda: F.compute_attention_scores(q, k), 30, 3)
+    n = CFG2["Hq"] * CFG2["S"]
+    add("cfg2", "compute_attention_scores", ms, 2 * n * CFG2["S"] * CFG2["D"], 2 * n * CFG2["D"] * 2 + n * CFG2["S"] * 2)
+    del q, k
+
+    # decoding: few query rows against 16 384 keys; K/V traffic bounds it
+    for M in (1, 16):
+        dec = dict(B=4, Hq=32, Hk=8, D=128, N=16384)
+        g = torch.Generator(device=device).manual_seed(M)
+        q = torch.randn(dec["B"], dec["Hq"], M, dec["D"], device=device, generator=g).half()
+        k = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
+        v = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
+        kv_bytes = 2 * dec["B"] * dec["Hk"] * dec["N"] * dec["D"] * 2
+        flops = 4 * dec["B"] * dec["Hq"] * M * dec["N"] * dec["D"]
+        for label, splits in (("attention split-KV", None), ("attention unsplit", 1)):
+            ms = time_op(lambda: F.attention(q, k, v, False, kv_splits=splits), 30, 3)
+            add(f"decode M={M} N=16384 B=4 Hq=32 Hk=8", label, ms, flops, kv_bytes + 2 * q.numel() * 2)
+        del q, k, v
+    return rows
+
+
+CFG4 = dict(B=2, Hq=32, Hk=8, S=4096, D=128, dtype=torch.float16, causal=True, split=3072)
+CFG5 = dict(B=4, Hq=32, Hk=8, S=16384, D=128, dtype=torch.bfloat16, causal=False, vdist="uniform", split=12288)
+
+
+def _max_over_ranks(x, device, world):
+    import torch.distributed as dist
+    t = torch.tensor([x], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def _all_true(flag, device, world):
+    import torch.distributed as dist
+    t = torch.tensor([1.0 if flag else 0.0], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item() > 0.5)
+
+
+def make_unit(cfg, unit, seed, device):
+    """q (1,G,S,D), k, v (1,1,S,D) of shard unit `unit` = b*Hk + hk, drawn on the device from seed + unit:
+    any rank can build any unit without the others."""
+    G, S, D = cfg["Hq"] // cfg["Hk"], cfg["S"], cfg["D"]
+    g = torch.Generator(device=device).manual_seed(seed + unit)
+    q = torch.randn(1, G, S, D, device=device, generator=g)
+    k = torch.randn(1, 1, S, D, device=device, generator=g)
+    if cfg.get("vdist") == "uniform":
+        v = torch.rand(1, 1, S, D, device=device, generator=g) * 2 - 1
+    else:
+        v = torch.randn(1, 1, S, D, device=device, generator=g)
+    return q.to(cfg["dtype"]), k.to(cfg["dtype"]), v.to(cfg["dtype"])
+
+
+def _time_calls(fn, iters, warmup, device, world):
+    """Mean ms per call over `iters` back-to-back calls, CUDA events, barrier on both sides, max over ranks."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    return _max_over_ranks(a.elapsed_time(b) / iters, device, world)
+
+
+def unit_shard_leg(F, device, rank, world, pk):
+    """The partition the path shards by: (batch, kv head) units with their G query heads, dealt to the
+    ranks in contiguous blocks (shard.plan_units), no exchange step.  Strong scaling: the whole cfg4 / cfg5
+    problem at every N; each rank builds and runs only its units (as a batch of single-kv-head problems).
+    Device time, max over ranks; the one-GPU time of all units is measured in the same run on rank 0."""
+    from flash_attn_with_score_b200 import shard
+    rows = []
+    plans = [("cfg4", CFG4, "cross_qk", 20), ("cfg4", CFG4, "cross_softmax", 20), ("cfg5", CFG5, "softmax_col_sum", 3)]
+    cache = {}
+    for name, cfg, op, iters in plans:
+        n_units = cfg["B"] * cfg["Hk"]
+        mine = shard.plan_units(n_units, world)[rank]
+        G, S, split = cfg["Hq"] // cfg["Hk"], cfg["S"], cfg["split"]
+        if name not in cache:
+            cache.clear()
+            units = [make_unit(cfg, u, 0, device) for u in mine]
+            cache[name] = tuple(torch.cat([u[i] for u in units], 0) for i in range(3)) if units else None
+        local = cache[name]
+
+        def call(t):
+            q, k, v = t
+            if op == "cross_qk":
+                return F.attention_cross_token_qk_sum(q, k, v, split, cfg["causal"])
+            if op == "cross_softmax":
+                return F.attention_cross_token_softmax_sum(q, k, v, split, cfg["causal"])
+            return F.attention_with_softmax_col_sum(q, k, v, cfg["causal"])
+
+        ms = _time_calls((lambda: call(local)) if local is not None else (lambda: None), iters, 2, device, world)
+        # size-independent checks on this rank's units (torch fp64 on the device is the checker here)
+        ok = True
+        viol = 0.0
+        if local is not None:
+            q, k, v = local
+            out, sums = call(local)
+            if op == "cross_qk":  # linear identity: sum_i s_ij = sm_scale * k_j . sum_{i >= split} q_i (j < split <= i)
+                qs = q[:, :, split:].double().sum(2).sum(1)  # (units, D): rows >= split, all G heads
+                want = torch.einsum("und,ud->un", k[:, 0, :split].double(), qs) / math.sqrt(cfg["D"])
+                err = (sums[:, 0].double() - want).abs()
+                tol = 1e-3 * want.abs() + 1e-3 * want.pow(2).mean().sqrt()
+                viol = float((err - tol).max())
+            elif op == "softmax_col_sum":  # every query row spreads a total weight of 1 over the keys
+                total = sums.double().sum(-1)
+                viol = float(((total - G * S).abs() - 1e-3 * G * S).max())
+            else:  # cross_softmax: first query head of the first local unit against plain torch fp32
+                s = (q[0, 0, split:].float() @ k[0, 0].float().t()) / math.sqrt(cfg["D"])
+                if cfg["causal"]:
+                    i = torch.arange(split, S, device=device).unsqueeze(1)
+                    j = torch.arange(S, device=device).unsqueeze(0)
+                    s = s.masked_fill(j > i, float("-inf"))
+                w = torch.softmax(s, -1)[:, :split].double().sum(0)
+                _, per_head = F.attention_cross_token_softmax_sum(q[:1], k[:1], v[:1], split, cfg["causal"],
+                                                                  per_q_head=True)
+                err = (per_head[0, 0].double() - w).abs()
+                viol = float((err - (1e-3 * w.abs() + 1e-3 * w.pow(2).mean().sqrt())).max())
+            ok = viol <= 0
+        ok = _all_true(ok, device, world)
+        # all units on one GPU, same run (rank 0)
+        t1 = None
+        if world > 1 and rank == 0:
+            allu = [make_unit(cfg, u, 0, device) for u in range(n_units)]
+            full = tuple(torch.cat([u[i] for u in allu], 0) for i in range(3))
+            del allu
+            for _ in range(2):
+                call(full)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                call(full)
+            b.record()
+            torch.cuda.synchronize()
+            t1 = a.elapsed_time(b) / iters
+            del full
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        split_arg = split if op != "softmax_col_sum" else None
+        flops, _ = algorithmic(cfg, op, split_arg)
+        row = {"workload": name, "op": op, "scaling": "strong", "n_gpus": world, "units": n_units,
+               "units_per_rank": len(mine), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+               "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (world * pk["tensor"]), "parity_ok": ok,
+               "parity": {"cross_qk": "linear identity k_j . sum_i q_i", "softmax_col_sum": "mass conservation G*S per unit",
+                          "cross_softmax": "one query head against torch fp32 softmax"}[op]}
+        if world == 1:
+            row["one_gpu_ms"] = ms
+        elif t1 is not None:
+            row["one_gpu_ms"] = t1
+            row["efficiency"] = t1 / (world * ms)
+            per_unit = t1 / n_units
+            row["limiter"] = ("launch + fixed per-call cost: %.0f us of kernels per rank against ~%.0f us of per-call "
+                              "set-up and tail that does not shrink with the unit count"
+                              % (per_unit * len(mine) * 1e3, max(0.0, ms - per_unit * len(mine)) * 1e3))
+        rows.append(row)
+    cache.clear()
+    return rows
+
+
+def query_split_leg(F, device, rank, world, pk):
     """The one path with a collective: the query rows of every head of cfg5 are split over the ranks
     (K/V replicated), each rank runs attention_with_softmax_col_sum on its row window, the fp32
     partial column sums are all-gathered over NCCL and added in rank order on every rank.  Strong
-    scaling (the whole cfg5 problem at every N); device time, max over ranks."""
+    scaling (the whole cfg5 problem at every N); device time, max over ranks.  The exchange of batch
+    element b overlaps the kernels of element b + 1; the exposed part is total - compute-only."""
     import torch.distributed as dist
     from flash_attn_with_score_b200 import shard
-    cfg = dict(B=4, Hq=32, Hk=8, S=16384, D=128, dtype=torch.bfloat16, causal=False, vdist="uniform")
+    cfg = CFG5
     q, k, v = make_inputs(cfg, 0, device)  # same seed on every rank: identical tensors
+    G, S = cfg["Hq"] // cfg["Hk"], cfg["S"]
     steps = 3
-    shard.query_split(F.attention_with_softmax_col_sum, q, k, v, False)
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        out, sums, rows = shard.query_split(F.attention_with_softmax_col_sum, q, k, v, False)
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    begin, end = shard.plan_query_rows(S, world)[rank]
+    res = {}
+
+    def run_overlap():
+        res["v"] = shard.query_split(F.attention_with_softmax_col_sum, q, k, v, False, overlap=True)
+
+    def run_serial():
+        res["s"] = shard.query_split(F.attention_with_softmax_col_sum, q, k, v, False)
+
+    def run_compute_only():
+        for b in range(cfg["B"]):
+            F.attention_with_softmax_col_sum(q[b:b + 1], k[b:b + 1], v[b:b + 1], False, q_rows=(begin, end))
+
+    ms = _time_calls(run_overlap, steps, 1, device, world)
+    ms_serial = _time_calls(run_serial, steps, 1, device, world)
+    ms_compute = _time_calls(run_compute_only, steps, 1, device, world)
+    out, sums, rows = res["v"]
+    # parity that is not rank-vs-rank: mass conservation per (b, kv head), and one kv head against the unsplit call
+    total = sums.double().sum(-1)
+    mass_viol = float(((total - G * S).abs() - 1e-3 * G * S).max())
+    _, one = F.attention_with_softmax_col_sum(q[:1, :G], k[:1, :1], v[:1, :1], False)
+    err = (sums[0, 0].double() - one[0, 0].double()).abs()
+    unsplit_viol = float((err - (1e-3 * one[0, 0].double().abs() + 1e-3 * one.double().pow(2).mean().sqrt())).max())
+    same_bits = torch.equal(res["s"][1], sums)
     digest = sums.double().sum().reshape(1)
     lo, hi = digest.clone(), digest.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    parity_ok = _all_true(mass_viol <= 0 and unsplit_viol <= 0 and same_bits, device, world)
     flops, _ = algorithmic(cfg, "softmax_col_sum", None)
-    ms = t.item()
     return {"workload": "cfg5", "op": "attention_with_softmax_col_sum", "scaling": "strong", "n_gpus": world,
-            "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps,
-            "rows_per_rank": rows[1] - rows[0],
-            "collective": "all_gather of the fp32 partial column sums + fixed-order reduce kernel",
+            "ms_per_step": ms, "ms_per_step_exchange_after_compute": ms_serial, "ms_compute_only": ms_compute,
+            "exposed_exchange_ms": max(0.0, ms - ms_compute),
+            "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps, "rows_per_rank": rows[1] - rows[0],
+            "collective": "per batch element: all_gather of the fp32 partial column sums (async, overlapping the next "
+                          "element's kernels) + fixed-order reduce kernel",
             "exchanged_bytes_per_rank": int(sums.numel() * 4 * (world - 1)),
             "sums_identical_on_all_ranks": bool((lo == hi).item()),
+            "parity_ok": parity_ok, "mass_conservation_viol": mass_viol, "vs_unsplit_one_kv_head_viol": unsplit_viol,
+            "overlapped_equals_serial_bits": bool(same_bits),
             "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (world * pk["tensor"])}
 
 
@@ -511,9 +730,38 @@ def main():
     h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv))
     d2h = h_out.numel() * h_out.element_size() + h_scores.numel() * 4
 
-    qsplit = None
-    if world > 1 and not args.no_ops:
-        qsplit = query_split_leg(F, device, world, pk)
+    # bare copies of the same byte counts on the same streams, all ranks at once: the ceiling of the e2e figure
+    def copy_only_step(i):
+        bset = i & 1
+        dq, dk, dv, dout, dscores = sets[bset]
+        with torch.cuda.stream(s_in):
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            h_out.copy_(dout, non_blocking=True)
+            h_scores.copy_(dscores, non_blocking=True)
+
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    s_in.wait_event(c0)
+    s_out.wait_event(c0)
+    for i in range(e2e_steps):
+        copy_only_step(i)
+    cur.wait_stream(s_in)
+    cur.wait_stream(s_out)
+    c1.record()
+    torch.cuda.synchronize()
+    copy_only_ms = _max_over_ranks(c0.elapsed_time(c1) / e2e_steps, device, world)
+
+    qsplit = ushard = None
+    if not args.no_ops:
+        ushard = unit_shard_leg(F, device, rank, world, pk)
+        if world > 1:
+            qsplit = query_split_leg(F, device, rank, world, pk)
 
     if rank != 0:
         if world > 1:
@@ -547,12 +795,16 @@ def main():
                      "kernel_event_ms": kern_ms, "frac_event": nbytes / (kern_ms * 1e-3) / 1e9 / pk["hbm"],
                      "step_event_ms": step_event_ms, "timing": launch_timing},
         "e2e": {"value": world * score_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "copy_only_ms": copy_only_ms,
+                "limiter": "host link: %.0f %% of the step is the bare H2D + D2H copies of the same bytes "
+                           "(all ranks copying at once)" % (100.0 * copy_only_ms / e2e_ms),
                 "pipeline": "two buffer sets; H2D, kernel and D2H of neighbouring steps overlap on three streams"},
         "gpu_launches": launches, "backend": F.last_backend(), "device_status": status, "clocks": clocks,
         "parity": parity,
     }
     line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES_PER_LAUNCH
+    if ushard is not None:
+        line["unit_shard"] = ushard
     if qsplit is not None:
         line["query_split"] = qsplit
     if world == 1 and not args.no_cpu:

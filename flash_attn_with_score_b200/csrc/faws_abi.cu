@@ -449,10 +449,11 @@ int faws_attention_backward(const faws_problem* p, const faws_grads* g, void* wo
   b.p_seq = p->N - p->M; b.causal = p->causal ? 1 : 0; b.sm_scale = p->sm_scale;
   b.drop = make_drop(p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (launch_bwd_delta(b, p->dtype, s) != cudaSuccess) return FAWS_ECUDA;
   bool use_tc = false;
   if (p->backend != FAWS_BACKEND_GENERIC) use_tc = tc_bwd_supported(b, p->dtype);
   if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc) return FAWS_EBACKEND;
+  // the tcgen05 path has its own pre-pass (delta and L into tile-padded arrays in the workspace)
+  if (!use_tc && launch_bwd_delta(b, p->dtype, s) != cudaSuccess) return FAWS_ECUDA;
   const cudaError_t e = use_tc ? launch_tc_bwd(b, p->dtype, s) : launch_generic_bwd(b, p->dtype, s);
   if (e != cudaSuccess) {
     std::fprintf(stderr, "faws: backward launch failed: %s\n", cudaGetErrorString(e));
@@ -468,8 +469,8 @@ size_t faws_workspace_bytes(int32_t op, const faws_problem* p, int32_t split) {
     case FAWS_OP_ATTENTION_SPLIT_KV:  // `split` carries the number of key ranges
       if (split < 1 || split > cdiv(p->N, kTcBlockN)) return 0;
       return split == 1 ? 0 : split_kv_bytes(p, split);
-    case FAWS_OP_ATTENTION_BACKWARD:
-      return align256((size_t)p->B * p->Hq * p->M * 4);
+    case FAWS_OP_ATTENTION_BACKWARD:  // enough for either kernel family
+      return tc_bwd_workspace_bytes(p->B, p->Hq, p->Hk, p->M, p->N, p->D);
     case FAWS_OP_COL_SUM:
     case FAWS_OP_COL_SUM_SEQUENTIAL:
       return align256(partial_floats(p, 0, p->N) * 4) + align256(qsum_floats(p) * 4);

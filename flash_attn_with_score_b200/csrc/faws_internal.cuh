@@ -203,7 +203,8 @@ bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p);
 cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, int group_sum, cudaStream_t s);
 
 bool tc_bwd_supported(const BwdParams& p, int dtype);
-cudaError_t launch_tc_bwd(const BwdParams& p, int dtype, cudaStream_t s);
+cudaError_t launch_tc_bwd(const BwdParams& p, int dtype, cudaStream_t s);  // p.delta = the workspace base
+size_t tc_bwd_workspace_bytes(int B, int Hq, int Hk, int M, int N, int D);
 
 int tc_read_status(int reset);  // synchronising read of the device status word
 cudaError_t launch_wait_give_up(cudaStream_t s);  // self-test: a bounded wait that runs out
