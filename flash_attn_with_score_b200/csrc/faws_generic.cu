@@ -380,55 +380,79 @@ __global__ void __launch_bounds__(NT) generic_colsoftmax_kernel(ColSoftmaxParams
 
 // Second pass of the buffered cross-token variant: the scaled scores of the cross region were
 // stored by the forward pass as (B,Hq,M-split,split) fp32; this kernel streams them back
-// (attention_cross_token_softmax_sum.py:581-627, without atomics).  HBM-bound: a CTA owns 128
-// key columns, 4 row groups x 128 threads read rows i = split + rg, +4, ... (coalesced 512 B
-// per warp and row, 4 independent loads in flight per thread), accumulate
-// exp(s - L_i) in registers and are added in the fixed order rg0+rg1+rg2+rg3.
-__global__ void __launch_bounds__(512) scratch_colsum_kernel(ColSoftmaxParams p, int heads_per_cta, int Hout) {
-  __shared__ float red[3][128];
-  const int col = threadIdx.x & 127, rg = threadIdx.x >> 7;
-  const int j = blockIdx.x * 128 + col;
+// (attention_cross_token_softmax_sum.py:581-627, without atomics).  HBM-bound, so it is built to keep
+// many bytes in flight: a CTA owns 128 key columns of one output head; a thread owns 4 adjacent columns
+// (one 16-byte load per row) and one of 8 row groups, and issues 8 independent row loads before it
+// uses any (32 threads x 8 row groups x 8 rows x 16 B = 32 KB in flight per CTA).  The exponentials are
+// accumulated per thread in registers and the 8 row groups are added in a fixed order at the end.
+constexpr int kScRowGroups = 8;
+constexpr int kScUnroll = 8;
+
+__global__ void __launch_bounds__(32 * kScRowGroups) scratch_colsum_kernel(ColSoftmaxParams p, int heads_per_cta, int Hout) {
+  __shared__ float4 red[kScRowGroups - 1][32];
+  const int ct = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int j0 = blockIdx.x * 128 + ct * 4;  // first of this thread's 4 columns
   const int ho = blockIdx.y, b = blockIdx.z;
   const int i_lo = max(max(p.i_begin, p.m_begin), p.split);
-  const bool col_ok = j < p.n_end && j < p.split;
   const int rows = p.M - p.split;
-  float acc = 0.f;
+  const int n_lim = min(p.n_end, p.split);
+  const bool vec_ok = (p.split % 4 == 0) && (j0 + 3 < n_lim);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int g = 0; g < heads_per_cta; ++g) {
     const int h = ho * heads_per_cta + g;
     const int64_t bh = (int64_t)b * p.Hq + h;
-    const float* sbase = p.s_scratch + bh * (int64_t)rows * p.split + j;
+    const float* sbase = p.s_scratch + bh * (int64_t)rows * p.split;
     const float* Lbase = p.L + bh * p.M;
-    // key j is visible to query i iff j <= i + p_seq
-    int i0 = i_lo;
-    if (p.causal) i0 = max(i0, j - p.p_seq);
-    // rows of this row group: i = i_start, i_start + 4, ...
-    int i = i0 + ((rg - i0) & 3);
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-    if (col_ok) {
-      for (; i + 12 < p.m_end; i += 16) {
-        const float s0 = __ldg(sbase + (int64_t)(i - p.split) * p.split);
-        const float s1 = __ldg(sbase + (int64_t)(i + 4 - p.split) * p.split);
-        const float s2 = __ldg(sbase + (int64_t)(i + 8 - p.split) * p.split);
-        const float s3 = __ldg(sbase + (int64_t)(i + 12 - p.split) * p.split);
-        const float L0 = Lbase[i], L1 = Lbase[i + 4], L2 = Lbase[i + 8], L3 = Lbase[i + 12];
-        a0 += (L0 == FAWS_NEG_INF) ? 0.f : exp2f((s0 - L0) * kLog2e);
-        a1 += (L1 == FAWS_NEG_INF) ? 0.f : exp2f((s1 - L1) * kLog2e);
-        a2 += (L2 == FAWS_NEG_INF) ? 0.f : exp2f((s2 - L2) * kLog2e);
-        a3 += (L3 == FAWS_NEG_INF) ? 0.f : exp2f((s3 - L3) * kLog2e);
+    // key j is visible to query i iff j <= i + p_seq: rows before i_first see none of this CTA's columns
+    int i_first = i_lo;
+    if (p.causal) i_first = max(i_first, blockIdx.x * 128 - p.p_seq);
+    for (int i0 = i_first + rg * kScUnroll; i0 < p.m_end; i0 += kScRowGroups * kScUnroll) {
+      float4 sv[kScUnroll];
+      float Lv[kScUnroll];
+#pragma unroll
+      for (int r = 0; r < kScUnroll; ++r) {  // loads first: eight rows in flight per thread
+        const int i = i0 + r;
+        sv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        Lv[r] = FAWS_NEG_INF;
+        if (i < p.m_end) {
+          const float* rowp = sbase + (int64_t)(i - p.split) * p.split + j0;
+          if (vec_ok) {
+            sv[r] = __ldcs(reinterpret_cast<const float4*>(rowp));  // streamed once
+          } else {
+            if (j0 < n_lim) sv[r].x = rowp[0];
+            if (j0 + 1 < n_lim) sv[r].y = rowp[1];
+            if (j0 + 2 < n_lim) sv[r].z = rowp[2];
+            if (j0 + 3 < n_lim) sv[r].w = rowp[3];
+          }
+          Lv[r] = Lbase[i];
+        }
       }
-      for (; i < p.m_end; i += 4) {
-        const float s0 = __ldg(sbase + (int64_t)(i - p.split) * p.split);
-        const float L0 = Lbase[i];
-        a0 += (L0 == FAWS_NEG_INF) ? 0.f : exp2f((s0 - L0) * kLog2e);
+#pragma unroll
+      for (int r = 0; r < kScUnroll; ++r) {
+        const int i = i0 + r;
+        if (Lv[r] == FAWS_NEG_INF) continue;  // row outside the window, or a row without a visible key
+        const float nl = -Lv[r] * kLog2e;
+        const int jmax = p.causal ? i + p.p_seq : 0x7fffffff;  // last visible key of this row
+        acc.x += (j0 <= jmax) ? exp2f(fmaf(sv[r].x, kLog2e, nl)) : 0.f;
+        acc.y += (j0 + 1 <= jmax) ? exp2f(fmaf(sv[r].y, kLog2e, nl)) : 0.f;
+        acc.z += (j0 + 2 <= jmax) ? exp2f(fmaf(sv[r].z, kLog2e, nl)) : 0.f;
+        acc.w += (j0 + 3 <= jmax) ? exp2f(fmaf(sv[r].w, kLog2e, nl)) : 0.f;
       }
     }
-    acc += (a0 + a1) + (a2 + a3);
   }
-  if (rg > 0) red[rg - 1][col] = acc;
+  if (rg > 0) red[rg - 1][ct] = acc;
   __syncthreads();
-  if (rg == 0 && col_ok) {
-    const float total = ((acc + red[0][col]) + red[1][col]) + red[2][col];
-    p.out[((int64_t)b * Hout + ho) * p.n_end + j] = total;
+  if (rg == 0) {
+#pragma unroll
+    for (int w = 0; w < kScRowGroups - 1; ++w) {  // row groups 0, 1, 2, ... in this order
+      const float4 o = red[w][ct];
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
+    float* dst = p.out + ((int64_t)b * Hout + ho) * p.n_end + j0;
+    if (j0 < n_lim) dst[0] = acc.x;
+    if (j0 + 1 < n_lim) dst[1] = acc.y;
+    if (j0 + 2 < n_lim) dst[2] = acc.z;
+    if (j0 + 3 < n_lim) dst[3] = acc.w;
   }
 }
 
@@ -689,7 +713,7 @@ cudaError_t launch_scratch_colsum(const ColSoftmaxParams& p, int group_sum, cuda
   const int hpc = group_sum ? p.G : 1;
   const int Hout = p.Hq / hpc;
   dim3 grid((p.n_end + 127) / 128, Hout, p.B);
-  scratch_colsum_kernel<<<grid, 512, 0, s>>>(p, hpc, Hout);
+  scratch_colsum_kernel<<<grid, 32 * kScRowGroups, 0, s>>>(p, hpc, Hout);
   count_launch();
   return cudaGetLastError();
 }
