@@ -306,7 +306,7 @@ def extra_rows(F, device, pk):
 
     # decoding: few query rows against 16 384 keys; K/V traffic bounds it
     for M in (1, 16):
-        dec = dict(B=4, Hq=32, Hk=8, D=128, N=16384)
+        dec = dict(B=1, Hq=32, Hk=8, D=128, N=16384)  # 32 CTAs unsplit: the split-KV plan cuts the keys into ranges
         g = torch.Generator(device=device).manual_seed(M)
         q = torch.randn(dec["B"], dec["Hq"], M, dec["D"], device=device, generator=g).half()
         k = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
@@ -315,7 +315,7 @@ def extra_rows(F, device, pk):
         flops = 4 * dec["B"] * dec["Hq"] * M * dec["N"] * dec["D"]
         for label, splits in (("attention split-KV", None), ("attention unsplit", 1)):
             ms = time_op(lambda: F.attention(q, k, v, False, kv_splits=splits), 30, 3)
-            add(f"decode M={M} N=16384 B=4 Hq=32 Hk=8", label, ms, flops, kv_bytes + 2 * q.numel() * 2)
+            add(f"decode M={M} N=16384 B=1 Hq=32 Hk=8", label, ms, flops, kv_bytes + 2 * q.numel() * 2)
         del q, k, v
     return rows
 

@@ -111,8 +111,12 @@ int run_colsoftmax(const faws_problem* p, ColSoftmaxParams& c, float* final_out,
   if (p->backend == FAWS_BACKEND_TCGEN05 && !use_tc && c.s_scratch == nullptr) return FAWS_EBACKEND;
   cudaError_t e;
   if (c.s_scratch != nullptr) {  // buffered variant: stream the stored scores back
-    c.out = final_out;
-    e = launch_scratch_colsum(c, group_sum, s);
+    // one CTA per (128 keys, query head): G times more CTAs in flight than walking the group inside
+    // the CTA, which this bandwidth-bound pass needs; the G heads are added afterwards
+    const bool direct = !group_sum || c.G == 1;
+    c.out = direct ? final_out : per_head_ws;
+    e = launch_scratch_colsum(c, 0, s);
+    if (e == cudaSuccess && !direct) e = launch_group_sum(per_head_ws, final_out, c.B, c.Hk, c.G, c.n_end, s);
   } else if (use_tc) {
     const bool in_kernel = !group_sum || tc_colsoftmax_group_in_kernel(c);
     c.out = in_kernel ? final_out : per_head_ws;

@@ -388,6 +388,12 @@ __global__ void __launch_bounds__(NT) generic_colsoftmax_kernel(ColSoftmaxParams
 constexpr int kScRowGroups = 8;
 constexpr int kScUnroll = 8;
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __global__ void __launch_bounds__(32 * kScRowGroups) scratch_colsum_kernel(ColSoftmaxParams p, int heads_per_cta, int Hout) {
   __shared__ float4 red[kScRowGroups - 1][32];
   const int ct = threadIdx.x & 31, rg = threadIdx.x >> 5;
@@ -405,7 +411,7 @@ __global__ void __launch_bounds__(32 * kScRowGroups) scratch_colsum_kernel(ColSo
     const float* Lbase = p.L + bh * p.M;
     // key j is visible to query i iff j <= i + p_seq: rows before i_first see none of this CTA's columns
     int i_first = i_lo;
-    if (p.causal) i_first = max(i_first, blockIdx.x * 128 - p.p_seq);
+    if (p.causal) i_first = max(i_first, (int)blockIdx.x * 128 - p.p_seq);  // signed: p_seq may exceed the tile start
     for (int i0 = i_first + rg * kScUnroll; i0 < p.m_end; i0 += kScRowGroups * kScUnroll) {
       float4 sv[kScUnroll];
       float Lv[kScUnroll];
@@ -433,10 +439,10 @@ __global__ void __launch_bounds__(32 * kScRowGroups) scratch_colsum_kernel(ColSo
         if (Lv[r] == FAWS_NEG_INF) continue;  // row outside the window, or a row without a visible key
         const float nl = -Lv[r] * kLog2e;
         const int jmax = p.causal ? i + p.p_seq : 0x7fffffff;  // last visible key of this row
-        acc.x += (j0 <= jmax) ? exp2f(fmaf(sv[r].x, kLog2e, nl)) : 0.f;
-        acc.y += (j0 + 1 <= jmax) ? exp2f(fmaf(sv[r].y, kLog2e, nl)) : 0.f;
-        acc.z += (j0 + 2 <= jmax) ? exp2f(fmaf(sv[r].z, kLog2e, nl)) : 0.f;
-        acc.w += (j0 + 3 <= jmax) ? exp2f(fmaf(sv[r].w, kLog2e, nl)) : 0.f;
+        acc.x += (j0 <= jmax) ? ex2_approx(fmaf(sv[r].x, kLog2e, nl)) : 0.f;
+        acc.y += (j0 + 1 <= jmax) ? ex2_approx(fmaf(sv[r].y, kLog2e, nl)) : 0.f;
+        acc.z += (j0 + 2 <= jmax) ? ex2_approx(fmaf(sv[r].z, kLog2e, nl)) : 0.f;
+        acc.w += (j0 + 3 <= jmax) ? ex2_approx(fmaf(sv[r].w, kLog2e, nl)) : 0.f;
       }
     }
   }

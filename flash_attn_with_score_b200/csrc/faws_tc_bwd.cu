@@ -15,6 +15,8 @@
 //
 // The 128 streamed rows are processed as two halves of 64 with their own TMEM columns, each by
 // its own consumer warpgroup, so the tensor pipe works on one half while the other is in registers.
+// (Measured alternatives, both slower on the same box: four parts of 32 with four consumer
+// warpgroups, 1.5-1.7x; S' and dP' as full 128-column MMAs handed back in four chunks, 1.15-1.25x.)
 // Warp roles (12 warps): warp 0 TMA producer (X, Y once, then a 2-stage ring of (A, B) pairs and,
 // key-major, the L / delta vectors of the streamed query tile), warp 1 TMEM allocation and the
 // MMA-issuing lane, warps 4-7 / 8-11 consumers of half 0 / 1 (thread = owned row = TMEM lane).

@@ -183,6 +183,8 @@ int faws_attention_with_col_sum(const faws_problem* p, float* col_sum, int32_t p
  *    FAWS_NOALLOC_SCRATCH_BYTES.
  *  - Calls no cudaMalloc / cudaFree / allocating routine.  The first call on a device
  *    resolves the array's address once; make it before any stream capture.
+ *  - The array that is used is the current device's: make the device that holds the tensors
+ *    current before the call (the same rule as for every other entry point's launches).
  *  - All calls on a device share the array: calls whose kernels may overlap on the GPU
  *    race; order them on one stream or with events.  Nothing needs to be zeroed between
  *    calls (each call writes every partial it later reads).
