@@ -616,6 +616,15 @@ def main():
         dist.barrier()
     torch.cuda.synchronize()
 
+    # warm-up of the timed mechanism itself: the W warm-up steps again, as graph replays
+    if graph is not None:
+        for _ in range(max(1, -(-args.warmup // N_SETS))):
+            graph.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()

@@ -158,13 +158,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   // slowest, so the heaviest row blocks of every head are dispatched first (longest-processing-
   // time-first packing of the causal triangle onto the SMs).
   // fill_ctas (score hooks, causal): the row-block axis holds two CTAs per row block, a compute
-  // CTA and a fill CTA that only writes the row block's never-visited key tiles; interleaved so
-  // that their costs decrease together (heaviest compute block, most-masked fill block, ...).
+  // CTA and a fill CTA that only writes the row block's never-visited key tiles.  All compute
+  // CTAs come first in launch order (heaviest first), the fill CTAs after them (most-masked row
+  // block first): measured against interleaving the two kinds, cfg2 runs 2 % faster.
   const int slot = (int)(p.lpt_order ? blockIdx.z : blockIdx.x);
   const int ncb = (int)(p.lpt_order ? gridDim.z : gridDim.x) >> (p.fill_ctas ? 1 : 0);
-  const bool is_fill = p.fill_ctas && (slot & 1);
-  const int cb_slot = p.fill_ctas ? (slot >> 1) : slot;
-  const int cb_rel = is_fill ? cb_slot : ncb - 1 - cb_slot;  // heaviest (last) blocks first
+  const bool is_fill = p.fill_ctas && slot >= ncb;
+  const int cb_rel = is_fill ? slot - ncb : ncb - 1 - slot;  // compute: heaviest (last) blocks first
   const int h = p.lpt_order ? blockIdx.x : blockIdx.y;
   // Split-KV launches (n_splits > 1) fold the key-range index into the batch axis of the grid.
   const int bz = p.lpt_order ? blockIdx.y : blockIdx.z;
