@@ -903,11 +903,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 //   out[j] = sum over heads of the CTA and queries i of exp(s_ij - L_i).
 // One CTA owns 128 keys of one (batch, kv head or query head) and walks the query tiles of its
 // heads.  S^T = K.Q^T puts keys on TMEM lanes, so thread j accumulates column j in a register:
-// no cross-thread reduction, fixed order, one store.  The pass is bound by the exponential
-// (MUFU) pipe, which a warp keeps busy only between its waits and TMEM loads, so the kernel runs
-// CS_WGS = 4 consumer warpgroups (16 warps, 4 per scheduler): warpgroup w owns S^T buffer w and Q
-// slot w, takes every fourth query tile in chunks of CS_CHUNK columns (that many live score
-// registers), and the partial sums are added in a fixed order at the end.
+// no cross-thread reduction, fixed order, one store.
+// One CTA owns CS_KT = 2 key tiles (256 keys) of one (batch, kv head or query head): every Q tile
+// it streams feeds two MMAs, which halves the Q traffic from L2 (32 KB per 128^3 MMA otherwise).
+// (Measured: 1-3 % faster, not more: halving the Q traffic, and, in a separate experiment, moving half of
+// the exponentials from the MUFU pipe to a cubic on the FMA pipe, both left the pass where it was.)
+// Four consumer warpgroups: warpgroup w owns S^T buffer w = key tile (w & 1) of the query tiles
+// of parity (w >> 1); it walks its tiles in chunks of CS_CHUNK columns (that many live score
+// registers); the two partial sums of a key tile are added in a fixed order at the end.
+constexpr int CS_KT = 2;
 constexpr int CS_WGS = 4;
 constexpr int CS_QSLOTS = CS_WGS;
 constexpr int CS_CHUNK = 64;  // score columns a consumer thread holds at a time
@@ -917,17 +921,17 @@ constexpr int CS_REGS_AUX = 56;
 constexpr int CS_REGS_CONSUMER = ((CS_REGS_LAUNCH * CS_THREADS - 128 * CS_REGS_AUX) / (CS_WGS * 128)) & ~7;
 static_assert(128 * CS_REGS_AUX + CS_WGS * 128 * CS_REGS_CONSUMER <= CS_REGS_LAUNCH * CS_THREADS,
               "setmaxnreg would block");
-static_assert(CS_QSLOTS == CS_WGS, "a warpgroup owns the slot and buffer of its index");
+static_assert(CS_WGS == 2 * CS_KT, "buffer w = key tile (w & 1) of query-tile parity (w >> 1)");
 
 template <int D>
 struct CsSmem {
   static constexpr int kTile = 128 * D * 2;
   static constexpr int kSub = 128 * 128;
-  static constexpr int k_off = 0;
-  static constexpr int q_off = k_off + kTile;
+  static constexpr int k_off = 0;                           // CS_KT key tiles
+  static constexpr int q_off = k_off + CS_KT * kTile;
   static constexpr int l_off = q_off + CS_QSLOTS * kTile;  // [warpgroup][2][128] floats: -L_i*log2e per query
-  static constexpr int comb_off = l_off + CS_WGS * 2 * 128 * 4;  // [warpgroup 1..][128] floats
-  static constexpr int bar_off = comb_off + (CS_WGS - 1) * 128 * 4;
+  static constexpr int comb_off = l_off + CS_WGS * 2 * 128 * 4;  // [key tile][128] floats
+  static constexpr int bar_off = comb_off + CS_KT * 128 * 4;
   static constexpr int total = bar_off + 256;
   static constexpr int alloc = total + 1024;
 };
@@ -935,7 +939,7 @@ struct CsSmem {
 struct CsBars {
   uint64_t k_full;
   uint64_t q_full[CS_QSLOTS], q_empty[CS_QSLOTS];
-  uint64_t s_full[CS_QSLOTS], s_free[CS_QSLOTS];
+  uint64_t s_full[CS_WGS], s_free[CS_WGS];  // per S^T buffer
   uint64_t l_ready[CS_WGS];
   uint32_t tmem_base;
   int abort_flag;
@@ -961,14 +965,15 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Causal: key tiles are the slowest grid dimension, so the key tiles that see the most queries
   // (the first ones) of all heads are dispatched first.  Otherwise key tiles are fastest.
-  const int n0 = (p.causal ? blockIdx.z : blockIdx.x) * BN;
+  const int n0 = (p.causal ? blockIdx.z : blockIdx.x) * (CS_KT * BN);  // first key of the CTA's CS_KT key tiles
   const int ho = p.causal ? blockIdx.x : blockIdx.y;
   const int b = p.causal ? blockIdx.y : blockIdx.z;
   const int n_heads_out = p.causal ? gridDim.x : gridDim.y;
   const int h0 = ho * heads_per_cta;  // first query head of this CTA
   const int hk = h0 / p.G;
 
-  // query tiles (absolute multiples of 128) this key tile needs, per head
+  // query tiles (absolute multiples of 128) the CTA's first key tile needs, per head (the second key tile
+  // sees a suffix of them; what it does not see is masked)
   const int i_lo = max(p.i_begin, p.m_begin);
   int i_first = i_lo;
   if (p.causal) i_first = max(i_first, n0 - p.p_seq);
@@ -981,10 +986,12 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
     for (int s = 0; s < CS_QSLOTS; ++s) {
       mbar_init(&bars->q_full[s], 1);
       mbar_init(&bars->q_empty[s], 1);
-      mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->s_free[s], 128);
     }
-    for (int w = 0; w < CS_WGS; ++w) mbar_init(&bars->l_ready[w], 128);
+    for (int w = 0; w < CS_WGS; ++w) {
+      mbar_init(&bars->s_full[w], 1);
+      mbar_init(&bars->s_free[w], 128);
+      mbar_init(&bars->l_ready[w], 128);
+    }
     bars->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&maps.q);
@@ -1004,9 +1011,10 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
     reg_dealloc<CS_REGS_AUX>();
     if (warp == 0 && lane == 0 && total > 0) {
       // ---------------------------------------------------------- TMA producer
-      mbar_arrive_expect_tx(&bars->k_full, L::kTile);
-      for (int c = 0; c < D / 64; ++c)
-        tma_load_4d(smem + L::k_off + c * L::kSub, &maps.k, &bars->k_full, c * 64, n0, hk, b);
+      mbar_arrive_expect_tx(&bars->k_full, CS_KT * L::kTile);
+      for (int kt = 0; kt < CS_KT; ++kt)
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::k_off + kt * L::kTile + c * L::kSub, &maps.k, &bars->k_full, c * 64, n0 + kt * BN, hk, b);
       for (int u = 0; u < total; ++u) {
         const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
         const int g = u / ntq, qt = qt0 + (u - g * ntq);
@@ -1026,20 +1034,26 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       bool ok = mbar_wait(&bars->k_full, 0, abort_flag);
       for (int u = 0; ok && u < total; ++u) {
         const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
+        const int buf0 = (u & 1) * CS_KT, buse = u >> 1;  // S^T buffers of this query tile, and their use count
         if (!(ok = mbar_wait(&bars->q_full[s], use & 1, abort_flag))) break;
-        if (!(ok = mbar_wait(&bars->s_free[s], (use & 1) ^ 1, abort_flag))) break;
+        for (int kt = 0; ok && kt < CS_KT; ++kt) ok = mbar_wait(&bars->s_free[buf0 + kt], (buse & 1) ^ 1, abort_flag);
+        if (!ok) break;
         tc_fence_after();
         const uint64_t qd = q_desc0 + (uint64_t)(s * (L::kTile >> 4));
-        const uint32_t d_tmem = tmem_base + (uint32_t)(s * BM);
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
-            if (kk == 0) mma_ss(d_tmem, k_desc + off, qd + off, idesc, 0u);
-            else mma_ss_acc(d_tmem, k_desc + off, qd + off, idesc);
+          for (int kt = 0; kt < CS_KT; ++kt) {
+            const uint32_t d_tmem = tmem_base + (uint32_t)((buf0 + kt) * BM);
+            const uint64_t kd = k_desc + (uint64_t)(kt * (L::kTile >> 4));
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
+              if (kk == 0) mma_ss(d_tmem, kd + off, qd + off, idesc, 0u);
+              else mma_ss_acc(d_tmem, kd + off, qd + off, idesc);
+            }
+            if (kt == CS_KT - 1) mma_commit(&bars->q_empty[s]);
+            mma_commit(&bars->s_full[buf0 + kt]);
           }
-          mma_commit(&bars->q_empty[s]);
-          mma_commit(&bars->s_full[s]);
         }
         __syncwarp();
       }
@@ -1053,7 +1067,9 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
     const int wg = (warp - 4) >> 2;
     const int lg = warp & 3;
     const int row = lg * 32 + lane;
-    const int j = n0 + row;
+    const int kt = wg & (CS_KT - 1), par = wg / CS_KT;  // this warpgroup's key tile and query-tile parity
+    const int nk0 = n0 + kt * BN;                      // first key of that tile
+    const int j = nk0 + row;
     const uint32_t t_buf = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(wg * BM);
     const float scale_log2 = p.sm_scale * kLog2e;
 
@@ -1072,14 +1088,14 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 
     bool alive = true;
     int mine = 0;  // tiles this warpgroup has processed
-    float negl_next = (wg < total) ? load_negl(wg) : FAWS_NEG_INF;
-    for (int u = wg; u < total; u += CS_WGS, ++mine) {
+    float negl_next = (par < total) ? load_negl(par) : FAWS_NEG_INF;
+    for (int u = par; u < total; u += 2, ++mine) {
       // Two L buffers per warpgroup: the barrier below completes only when every thread of the
       // warpgroup has finished the previous tile, so the buffer of the tile before that is free.
       float* lb = lbuf + (wg * 2 + (mine & 1)) * 128;
       lb[row] = negl_next;
       mbar_arrive(&bars->l_ready[wg]);
-      if (u + CS_WGS < total) negl_next = load_negl(u + CS_WGS);
+      if (u + 2 < total) negl_next = load_negl(u + 2);
       if (!mbar_wait(&bars->l_ready[wg], mine & 1, abort_flag)) { alive = false; break; }
       if (!mbar_wait(&bars->s_full[wg], mine & 1, abort_flag)) { alive = false; break; }
       tc_fence_after();
@@ -1087,7 +1103,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       const int i0 = qt * BM;
       // causal: query column x is visible to key j iff i0 + x + p_seq >= j
       const int xlo = p.causal ? (j - p.p_seq - i0) : 0;
-      const bool full = !p.causal || (n0 + BN - 1 - p.p_seq - i0 <= 0);
+      const bool full = !p.causal || (nk0 + BN - 1 - p.p_seq - i0 <= 0);
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BM; c0 += CS_CHUNK) {
@@ -1132,20 +1148,18 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       acc += (a0 + a1) + (a2 + a3);
     }
     if (!alive) acc = 0.f;
-    if (wg > 0) comb[(wg - 1) * 128 + row] = acc;
+    if (par > 0) comb[kt * 128 + row] = acc;  // the odd query tiles' share of key tile kt
   }
 
   // ------------------------------------------------------------ common exit
   tc_fence_before();
   __syncthreads();
-  if (warp >= 4 && warp < 8) {
+  if (warp >= 4 && warp < 4 + 4 * CS_KT) {  // the even-parity warpgroup of each key tile writes it
     const int row = (warp & 3) * 32 + lane;
-    const int j = n0 + row;
-    if (j < p.n_end) {  // warpgroups 0, 1, 2, ... in this order
-      float total_sum = acc;
-#pragma unroll
-      for (int w = 0; w < CS_WGS - 1; ++w) total_sum += comb[w * 128 + row];
-      p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = total_sum;
+    const int kt = (warp - 4) >> 2;
+    const int j = n0 + kt * BN + row;
+    if (j < p.n_end) {  // even query tiles first, then the odd ones
+      p.out[((int64_t)b * n_heads_out + ho) * p.n_end + j] = acc + comb[kt * 128 + row];
     }
   }
   if (*abort_flag) {
@@ -1347,7 +1361,7 @@ int tc_read_status(int reset) {
 bool tc_colsoftmax_group_in_kernel(const ColSoftmaxParams& p) {
   if (p.G == 1) return true;
   const int sms = sm_count();
-  const long long ctas = (long long)((p.n_end + BN - 1) / BN) * p.Hk * p.B;
+  const long long ctas = (long long)((p.n_end + CS_KT * BN - 1) / (CS_KT * BN)) * p.Hk * p.B;
   return !(p.causal && ctas < 8LL * sms) && ctas >= 2LL * sms;
 }
 
@@ -1368,7 +1382,7 @@ cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads
   using L = CsSmem<D>;
   static PerDeviceOnce attr_once;
   if (cudaError_t e = set_max_smem_once(attr_once, tc_colsoftmax_kernel<T, D>, L::alloc); e != cudaSuccess) return e;
-  const int nkt = (p.n_end + BN - 1) / BN;
+  const int nkt = (p.n_end + CS_KT * BN - 1) / (CS_KT * BN);  // CTAs along the keys: CS_KT key tiles each
   dim3 grid = p.causal ? dim3(p.Hq / heads_per_cta, p.B, nkt) : dim3(nkt, p.Hq / heads_per_cta, p.B);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;

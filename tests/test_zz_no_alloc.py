@@ -26,9 +26,20 @@ def _noalloc_col_sum(q, k, v, causal, per_q_head=False):
     heads = call.H if per_q_head else call.Hk
     col = torch.full((call.B, heads, call.N), float("nan"), device=q.device, dtype=torch.float32)
     stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+    torch.cuda.synchronize()
+    free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
     rc = call.lib.faws_attention_with_col_sum_noalloc(C.byref(call.p), C.c_void_p(col.data_ptr()),
                                                       1 if per_q_head else 0, stream)
+    torch.cuda.synchronize()
+    # inputs and outputs were allocated above: the call itself must not take device memory from anyone
+    assert torch.cuda.memory_allocated() == held0
+    if not FIRST_CALL_ON_DEVICE[0]:
+        assert torch.cuda.mem_get_info()[0] == free0
+    FIRST_CALL_ON_DEVICE[0] = False  # (the very first launch of a kernel may load its module)
     return rc, call.out, col
+
+
+FIRST_CALL_ON_DEVICE = [True]
 
 
 def _inputs(shape, dtype, seed):
@@ -41,8 +52,12 @@ def _inputs(shape, dtype, seed):
 
 
 def test_two_calls_in_a_row_match_the_workspace_entry_point():
+    # the third case fills half of the built-in array, the fourth is a small causal problem that runs over
+    # whatever the third left there
     cases = [((1, 4, 2, 512, 128), torch.float16, True, False, 21),
-             ((2, 6, 2, 320, 64), torch.bfloat16, False, True, 22)]
+             ((2, 6, 2, 320, 64), torch.bfloat16, False, True, 22),
+             ((1, 16, 4, 2048, 64), torch.float16, False, False, 24),
+             ((1, 2, 2, 192, 64), torch.float16, True, False, 25)]
     for shape, dtype, causal, per_q_head, seed in cases:
         q, k, v = _inputs(shape, dtype, seed)
         rc, out, col = _noalloc_col_sum(q, k, v, causal, per_q_head)
