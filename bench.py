@@ -506,12 +506,14 @@ def query_split_leg(F, device, rank, world, pk):
     _, one = F.attention_with_softmax_col_sum(q[:1, :G], k[:1, :1], v[:1, :1], False)
     err = (sums[0, 0].double() - one[0, 0].double()).abs()
     unsplit_viol = float((err - (1e-3 * one[0, 0].double().abs() + 1e-3 * one.double().pow(2).mean().sqrt())).max())
-    same_bits = torch.equal(res["s"][1], sums)
+    same_bits = torch.equal(res["s"][1], sums)  # not required: per-element calls may pick another launch shape
+    d2 = (res["s"][1].double() - sums.double()).abs()
+    forms_viol = float((d2 - (1e-3 * sums.double().abs() + 1e-3 * sums.double().pow(2).mean().sqrt())).max())
     digest = sums.double().sum().reshape(1)
     lo, hi = digest.clone(), digest.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-    parity_ok = _all_true(mass_viol <= 0 and unsplit_viol <= 0 and same_bits, device, world)
+    parity_ok = _all_true(mass_viol <= 0 and unsplit_viol <= 0 and forms_viol <= 0, device, world)
     flops, _ = algorithmic(cfg, "softmax_col_sum", None)
     ms_overlap, ms = ms, min(ms, ms_serial)
     return {"workload": "cfg5", "op": "attention_with_softmax_col_sum", "scaling": "strong", "n_gpus": world,
@@ -525,7 +527,7 @@ def query_split_leg(F, device, rank, world, pk):
             "exchanged_bytes_per_rank": int(sums.numel() * 4 * (world - 1)),
             "sums_identical_on_all_ranks": bool((lo == hi).item()),
             "parity_ok": parity_ok, "mass_conservation_viol": mass_viol, "vs_unsplit_one_kv_head_viol": unsplit_viol,
-            "overlapped_equals_serial_bits": bool(same_bits),
+            "overlapped_vs_serial_viol": forms_viol, "overlapped_equals_serial_bits": bool(same_bits),
             "frac_of_tensor_peak_all_gpus": flops / (ms * 1e-3) / 1e12 / (world * pk["tensor"])}
 
 

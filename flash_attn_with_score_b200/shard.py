@@ -95,7 +95,9 @@ def query_split(op, q, k, v, *args, group=None, overlap=False, **kwargs):
 
     ``overlap=True`` walks the batch one element at a time and starts the all-gather of an element's
     partial sums as soon as they exist, so the exchange of element b runs on NCCL's stream while
-    the kernels of element b + 1 compute; the rank-order reduce follows at the end.  Same bits."""
+    the kernels of element b + 1 compute; the rank-order reduce follows at the end.  Deterministic like
+    the whole-batch form; the two forms agree to rounding (a one-element call may use another launch
+    shape, hence another fixed summation order inside a rank)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     begin, end = plan_query_rows(q.shape[2], world)[rank]
