@@ -15,8 +15,9 @@
 //
 // The 128 streamed rows are processed as two halves of 64 with their own TMEM columns, each by
 // its own consumer warpgroup, so the tensor pipe works on one half while the other is in registers.
-// (Measured alternatives, both slower on the same box: four parts of 32 with four consumer
-// warpgroups, 1.5-1.7x; S' and dP' as full 128-column MMAs handed back in four chunks, 1.15-1.25x.)
+// (Measured alternatives, all slower on the same box: four parts of 32 with four consumer
+// warpgroups, 1.5-1.7x; S' and dP' as full 128-column MMAs handed back in four chunks, 1.15-1.25x;
+// separate barriers for S' and dP' plus a hand-off per 32-column chunk, 1.1-1.2x.)
 // Warp roles (12 warps): warp 0 TMA producer (X, Y once, then a 2-stage ring of (A, B) pairs and,
 // key-major, the L / delta vectors of the streamed query tile), warp 1 TMEM allocation and the
 // MMA-issuing lane, warps 4-7 / 8-11 consumers of half 0 / 1 (thread = owned row = TMEM lane).
@@ -66,9 +67,8 @@ struct BwSmem {
 struct BwBars {
   uint64_t x_full;
   uint64_t r_full[NSTAGE], r_empty[NSTAGE];
-  uint64_t s_full[2];      // per half: S' written by the tensor pipe
-  uint64_t dp_full[2];     // per half: dP' written by the tensor pipe
-  uint64_t p_ready[2][2];  // per half and 32-column chunk: P' and dS' written by the half's 128 consumer threads
+  uint64_t s_full[2];   // per half: S' and dP' written by the tensor pipe
+  uint64_t p_ready[2];  // per half: P' and dS' written by its 128 consumer threads
   uint64_t acc_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -134,9 +134,7 @@ tc_bwd_kernel(const __grid_constant__ BwMaps maps, const BwTcParams p, int* __re
     }
     for (int e = 0; e < 2; ++e) {
       mbar_init(&bars->s_full[e], 1);
-      mbar_init(&bars->dp_full[e], 1);
-      mbar_init(&bars->p_ready[e][0], 128);
-      mbar_init(&bars->p_ready[e][1], 128);
+      mbar_init(&bars->p_ready[e], 128);
     }
     mbar_init(&bars->acc_done, 1);
     bars->abort_flag = 0;
@@ -206,19 +204,18 @@ tc_bwd_kernel(const __grid_constant__ BwMaps maps, const BwTcParams p, int* __re
             if (kk == 0) mma_ss(d_s, x_desc + off, a_rows + off, idesc1, 0u);
             else mma_ss_acc(d_s, x_desc + off, a_rows + off, idesc1);
           }
-          mma_commit(&bars->s_full[e]);  // the exponentials start while dP' is still being formed
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t off = (uint64_t)(((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4);
             if (kk == 0) mma_ss(d_dp, y_desc + off, b_rows + off, idesc1, 0u);
             else mma_ss_acc(d_dp, y_desc + off, b_rows + off, idesc1);
           }
-          mma_commit(&bars->dp_full[e]);
+          mma_commit(&bars->s_full[e]);
         }
         __syncwarp();
       };
       // accumulators (+)= the 16-bit operands of half e (in TMEM over S'_e / dP'_e) times the 64 streamed rows
-      auto issue_mma2 = [&](int e, int s, int chunk, bool first) {
+      auto issue_mma2 = [&](int e, int s, bool first) {
         const uint64_t a_tile = am_desc0 + (uint64_t)((s * 2 * L::kTile) >> 4);
         const uint64_t b_tile = a_tile + (uint64_t)(L::kTile >> 4);
         const uint32_t t_p = tmem_base + COL_S + (uint32_t)(e * HALF);    // P'_e: 64 values = 32 columns
@@ -226,10 +223,9 @@ tc_bwd_kernel(const __grid_constant__ BwMaps maps, const BwTcParams p, int* __re
         const uint32_t acc0 = tmem_base + COL_ACC, acc1 = tmem_base + COL_ACC + (uint32_t)D;
         if (elect_one()) {
 #pragma unroll
-          for (int kc = 0; kc < 2; ++kc) {
-            const int k4 = chunk * 2 + kc;  // the two K-steps (32 streamed rows) of this chunk
+          for (int k4 = 0; k4 < HALF / 16; ++k4) {
             const uint64_t off = (uint64_t)(((e * 4 + k4) * 16 * 128) >> 4);  // 16 streamed rows per K-step
-            const uint32_t accumulate = (first && kc == 0) ? 0u : 1u;
+            const uint32_t accumulate = (first && k4 == 0) ? 0u : 1u;
             if (KM) {
               mma_ts(acc0, t_p + (uint32_t)(k4 * 8), b_tile + off, idesc2, accumulate);   // dV += P^T . dout
               mma_ts(acc1, t_ds + (uint32_t)(k4 * 8), a_tile + off, idesc2, accumulate);  // dK += dS^T . Q
@@ -255,22 +251,19 @@ tc_bwd_kernel(const __grid_constant__ BwMaps maps, const BwTcParams p, int* __re
         const int s = u % NSTAGE;
         const bool more = u + 1 < nu;
         const int s1 = (u + 1) % NSTAGE;
-        for (int e = 0; ok && e < 2; ++e) {
-          for (int c = 0; ok && c < 2; ++c) {
-            if (!(ok = mbar_wait(&bars->p_ready[e][c], u & 1, abort_flag))) break;
-            tc_fence_after();
-            issue_mma2(e, s, c, u == 0 && e == 0 && c == 0);
-          }
-          if (!ok) break;
-          if (e == 1) commit(&bars->r_empty[s]);
-          if (more) {
-            if (e == 0) {
-              if (!(ok = mbar_wait(&bars->r_full[s1], ((u + 1) / NSTAGE) & 1, abort_flag))) break;
-              tc_fence_after();
-            }
-            issue_mma1(e, s1);  // S'_e of the next pair while the other half of this one is still in registers
-          }
+        if (!(ok = mbar_wait(&bars->p_ready[0], u & 1, abort_flag))) break;
+        tc_fence_after();
+        issue_mma2(0, s, u == 0);
+        if (more) {
+          if (!(ok = mbar_wait(&bars->r_full[s1], ((u + 1) / NSTAGE) & 1, abort_flag))) break;
+          tc_fence_after();
+          issue_mma1(0, s1);  // S'_0 of the next pair while half 1 of this one is still in registers
         }
+        if (!(ok = mbar_wait(&bars->p_ready[1], u & 1, abort_flag))) break;
+        tc_fence_after();
+        issue_mma2(1, s, false);
+        commit(&bars->r_empty[s]);
+        if (more) issue_mma1(1, s1);
       }
       if (ok) commit(&bars->acc_done);
     }
@@ -297,6 +290,8 @@ tc_bwd_kernel(const __grid_constant__ BwMaps maps, const BwTcParams p, int* __re
       uint32_t sv[HALF], dv[HALF];
       tmem_ld32(t_s, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
       tmem_ld32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+      tmem_ld32(t_dp, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
+      tmem_ld32(t_dp + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
       tmem_wait_ld();
       const int str0 = (u0 + u) * BT + e * HALF;  // first streamed row of this half
       // causal: (query i, key j) is visible iff j <= i + p_seq.  Column x of the half is streamed row
@@ -309,60 +304,37 @@ tc_bwd_kernel(const __grid_constant__ BwMaps maps, const BwTcParams p, int* __re
       }
       const float* vl = reinterpret_cast<const float*>(smem + L::vec_off + (u % NSTAGE) * 1024) + e * HALF;
       const float* vd = vl + 128;
-      // P' from S' (overwrites sv in place) while the tensor pipe is still forming dP'
+      uint32_t pk[HALF / 2], dk[HALF / 2];
 #pragma unroll
       for (int x = 0; x < HALF; x += 4) {
-        float nl[4];
+        float nl[4], dl[4];
         if (KM) {
           const float4 a = *reinterpret_cast<const float4*>(vl + x);
+          const float4 d4 = *reinterpret_cast<const float4*>(vd + x);
           nl[0] = a.x; nl[1] = a.y; nl[2] = a.z; nl[3] = a.w;
+          dl[0] = d4.x; dl[1] = d4.y; dl[2] = d4.z; dl[3] = d4.w;
         } else {
 #pragma unroll
-          for (int y = 0; y < 4; ++y) nl[y] = my_nl;
+          for (int y = 0; y < 4; ++y) { nl[y] = my_nl; dl[y] = my_dl; }
         }
+        float pr[4], ds[4];
 #pragma unroll
         for (int y = 0; y < 4; ++y) {
           const bool vis = (x + y >= x_lo) && (x + y <= x_hi);
           const float pe = fast_exp2(fmaf(__uint_as_float(sv[x + y]), c2, nl[y]));
-          sv[x + y] = __float_as_uint(vis ? pe : 0.f);
+          pr[y] = vis ? pe : 0.f;
+          ds[y] = pr[y] * (__uint_as_float(dv[x + y]) - dl[y]);
         }
+        pk[x / 2] = pack2<T>(pr[0], pr[1]);
+        pk[x / 2 + 1] = pack2<T>(pr[2], pr[3]);
+        dk[x / 2] = pack2<T>(ds[0], ds[1]);
+        dk[x / 2 + 1] = pack2<T>(ds[2], ds[3]);
       }
-      if (!mbar_wait(&bars->dp_full[e], u & 1, abort_flag)) { alive = false; break; }
-      tc_fence_after();
-      tmem_ld32(t_dp, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
-      tmem_ld32(t_dp + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
-      tmem_wait_ld();
-      // two chunks of 32 columns, each handed to the tensor pipe as soon as it is in TMEM
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16], dk[16];
-#pragma unroll
-        for (int x = 0; x < 32; x += 4) {
-          float dl[4];
-          if (KM) {
-            const float4 d4 = *reinterpret_cast<const float4*>(vd + c * 32 + x);
-            dl[0] = d4.x; dl[1] = d4.y; dl[2] = d4.z; dl[3] = d4.w;
-          } else {
-#pragma unroll
-            for (int y = 0; y < 4; ++y) dl[y] = my_dl;
-          }
-          float pr[4], ds[4];
-#pragma unroll
-          for (int y = 0; y < 4; ++y) {
-            pr[y] = __uint_as_float(sv[c * 32 + x + y]);
-            ds[y] = pr[y] * (__uint_as_float(dv[c * 32 + x + y]) - dl[y]);
-          }
-          pk[x / 2] = pack2<T>(pr[0], pr[1]);
-          pk[x / 2 + 1] = pack2<T>(pr[2], pr[3]);
-          dk[x / 2] = pack2<T>(ds[0], ds[1]);
-          dk[x / 2 + 1] = pack2<T>(ds[2], ds[3]);
-        }
-        if (KM) tmem_st16(t_s + (uint32_t)(c * 16), pk);  // P' is an operand only where dV is formed
-        tmem_st16(t_dp + (uint32_t)(c * 16), dk);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bars->p_ready[e][c]);
-      }
+      if (KM) tmem_st32(t_s, pk);  // P' is an operand only where dV is formed
+      tmem_st32(t_dp, dk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready[e]);
     }
 
     // ---- epilogue: accumulators -> 16-bit -> swizzled smem -> TMA store (clips at the tensor's edge)
