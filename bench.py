@@ -304,19 +304,21 @@ def extra_rows(F, device, pk):
     add("cfg2", "compute_attention_scores", ms, 2 * n * CFG2["S"] * CFG2["D"], 2 * n * CFG2["D"] * 2 + n * CFG2["S"] * 2)
     del q, k
 
-    # decoding: few query rows against 16 384 keys; K/V traffic bounds it
-    for M in (1, 16):
-        dec = dict(B=1, Hq=32, Hk=8, D=128, N=16384)  # 32 CTAs unsplit: the split-KV plan cuts the keys into ranges
-        g = torch.Generator(device=device).manual_seed(M)
-        q = torch.randn(dec["B"], dec["Hq"], M, dec["D"], device=device, generator=g).half()
-        k = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
-        v = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
-        kv_bytes = 2 * dec["B"] * dec["Hk"] * dec["N"] * dec["D"] * 2
-        flops = 4 * dec["B"] * dec["Hq"] * M * dec["N"] * dec["D"]
-        for label, splits in (("attention split-KV", None), ("attention unsplit", 1)):
-            ms = time_op(lambda: F.attention(q, k, v, False, kv_splits=splits), 30, 3)
-            add(f"decode M={M} N=16384 B=1 Hq=32 Hk=8", label, ms, flops, kv_bytes + 2 * q.numel() * 2)
-        del q, k, v
+    # decoding: few query rows against 16 384 keys; K/V traffic bounds it.  The G = 4 query heads of a kv head are
+    # packed into one query tile (K and V stream once per kv head) and the keys are cut into ranges (split-KV).
+    for B in (1, 4):
+        for M in (1, 16):
+            dec = dict(B=B, Hq=32, Hk=8, D=128, N=16384)
+            g = torch.Generator(device=device).manual_seed(M)
+            q = torch.randn(dec["B"], dec["Hq"], M, dec["D"], device=device, generator=g).half()
+            k = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
+            v = torch.randn(dec["B"], dec["Hk"], dec["N"], dec["D"], device=device, generator=g).half()
+            kv_bytes = 2 * dec["B"] * dec["Hk"] * dec["N"] * dec["D"] * 2
+            flops = 4 * dec["B"] * dec["Hq"] * M * dec["N"] * dec["D"]
+            for label, splits in (("attention split-KV", None), ("attention unsplit", 1)):
+                ms = time_op(lambda: F.attention(q, k, v, False, kv_splits=splits), 30, 3)
+                add(f"decode M={M} N=16384 B={B} Hq=32 Hk=8", label, ms, flops, kv_bytes + 2 * q.numel() * 2)
+            del q, k, v
     return rows
 
 

@@ -234,6 +234,29 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   return run_colsoftmax(p, c, sum_out, w.per_head, per_q_head ? 0 : 1, s);
 }
 
+// Decoding with grouped queries: when the G query heads of a kv head have so few rows that all of them
+// fit one 128-row tile, they are run as ONE head of G*M rows, so K and V are streamed once per kv head
+// instead of once per query head.  Pure re-indexing: row r = g*M + i of the packed head is row i of query
+// head hk*G + g, which for contiguous heads (stride_h == M * stride_s) is a plain row stride; out and L
+// index the same way.  Needs an unmasked problem (not causal, or a single query row, which sees every key).
+bool pack_gqa(const faws_problem* p, faws_problem* packed) {
+  const int G = p->Hq / p->Hk;
+  if (G <= 1 || (long long)G * p->M > kTcBlockM) return false;
+  if (p->causal && p->M != 1) return false;
+  if (p->causal && p->N < p->M) return false;
+  if (p->dropout_p > 0.f || p->m_begin != 0 || p->m_end != p->M) return false;
+  if (p->out.ptr == nullptr) return false;
+  if (p->q.stride_h != (int64_t)p->M * p->q.stride_s || p->out.stride_h != (int64_t)p->M * p->out.stride_s) return false;
+  *packed = *p;
+  packed->Hq = p->Hk;
+  packed->M = G * p->M;
+  packed->m_end = G * p->M;
+  packed->causal = 0;
+  packed->q.stride_h = p->q.stride_h * G;
+  packed->out.stride_h = p->out.stride_h * G;
+  return true;
+}
+
 // Number of key ranges for a problem that leaves most SMs idle: the plan of the reference's
 // num_splits_herustic (split_kv.py:234-262; its tiles are 16 x 128, here 128 x 128), i.e. the
 // smallest count whose wave efficiency is within 85 % of the best, among counts that leave no range
@@ -276,6 +299,11 @@ extern "C" {
 int faws_attention(const faws_problem* p, void* stream) {
   int st = validate(p);
   if (st != FAWS_OK) return st;
+  faws_problem packed;
+  if (p->backend != FAWS_BACKEND_GENERIC && pack_gqa(p, &packed)) {
+    FwdParams fp = make_fwd(&packed);
+    if (fp.v != nullptr && tc_fwd_supported(fp, packed.dtype)) p = &packed;
+  }
   FwdParams f = make_fwd(p);
   int bm, bn;
   return run_fwd(p, f, static_cast<cudaStream_t>(stream), &bm, &bn);
@@ -299,6 +327,11 @@ int32_t faws_split_kv_plan(const faws_problem* p) {
   if (validate(p) != FAWS_OK) return 1;
   if (p->dropout_p > 0.f || p->m_begin != 0 || p->m_end != p->M || p->backend == FAWS_BACKEND_GENERIC) return 1;
   if (p->v.ptr == nullptr || p->out.ptr == nullptr) return 1;
+  faws_problem packed;
+  if (pack_gqa(p, &packed)) {
+    FwdParams fp = make_fwd(&packed);
+    if (tc_fwd_supported(fp, packed.dtype)) p = &packed;
+  }
   FwdParams f = make_fwd(p);
   if (!tc_fwd_supported(f, p->dtype)) return 1;
   int dev = 0, sms = 148;
@@ -317,6 +350,11 @@ int faws_attention_split_kv(const faws_problem* p, int32_t n_splits, void* works
   if (n_splits == 1) return faws_attention(p, stream);
   if (workspace == nullptr || workspace_bytes < split_kv_bytes(p, n_splits)) return FAWS_EWORKSPACE;
   if (p->out.ptr == nullptr || p->v.ptr == nullptr) return FAWS_EINVAL;
+  faws_problem packed;  // same bytes of workspace either way: B*Hq*M is unchanged by the packing
+  if (p->backend != FAWS_BACKEND_GENERIC && pack_gqa(p, &packed)) {
+    FwdParams fp = make_fwd(&packed);
+    if (tc_fwd_supported(fp, packed.dtype)) p = &packed;
+  }
   FwdParams f = make_fwd(p);
   if (p->backend == FAWS_BACKEND_GENERIC || !tc_fwd_supported(f, p->dtype)) return FAWS_EBACKEND;
   float* L_part = static_cast<float*>(workspace);
