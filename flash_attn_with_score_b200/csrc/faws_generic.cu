@@ -490,10 +490,10 @@ __global__ void reduce_partials_kernel(ReducePartialParams p) {
 // Column sums with the linear part: a block owns one 128-wide key tile t of one output head.
 // out[j] = sm_scale * sum_h k_j . V_h(t) + sum_h sum_{qb hooked} partial[h][qb][j], where
 // V_h(t) = sum of qsum[h][qb] over the query tiles for which col_tile_linear(qb, t) holds.
-// Four thread groups of 128 work on four heads of the group at a time (the per-head chains of
+// Eight thread groups of 128 work on eight heads of the group at a time (the per-head chains of
 // dependent global loads are what the kernel waits for); their sums are combined in the fixed
-// order group 0..3 at the end.
-constexpr int kLinGroups = 4;
+// order group 0..7 at the end.
+constexpr int kLinGroups = 8;
 
 template <typename T>
 __global__ void __launch_bounds__(128 * kLinGroups) reduce_colsum_lin_kernel(ReducePartialParams p) {

@@ -232,9 +232,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     }
   }
 
+  // Round-robin: the key tiles in cyclic order from a start tile that differs from CTA to CTA
+  // (attention_with_col_sum_sequential.py:116-122), walked downwards.  Causal CTAs start at their last key
+  // tile, the one only the second query tile visits, so that this lone step overlaps the CTA's set-up
+  // instead of stalling the two-tile pipeline in mid-loop (a start in mid-range measured 10 % slower on
+  // cfg3, an upward walk 5 %); the causal round-robin walk is then the reverse order itself.
+  const int rr_start = p.causal ? nt - 1 : cb_abs % max(nt, 1);
   auto tile_of = [&](int it) -> int {
     if (p.schedule == kReverse) return kt0 + nt - 1 - it;
-    if (p.schedule == kRoundRobin) return kt0 + (cb_abs + it) % nt;
+    if (p.schedule == kRoundRobin) return kt0 + (rr_start - it + nt) % nt;
     return kt0 + it;
   };
   // K(0), V(0), K(1), V(1), ... go through the ring in this order
@@ -703,7 +709,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         // reduced here.
         const bool lin = p.col_lin != 0 &&
                          col_tile_linear(qb128, n0 / BN, p.col_row_lo, p.m_end, p.N, p.causal, p.p_seq);
-        if (!lin) {
+        // Nothing to do either where no partial is kept: query tiles before the first contributing row
+        // (cross-token sums: rows below the split) and key tiles beyond the summed columns.
+        if (!lin && part_on && n0 < p.ncols_pad) {
           const bool contrib = row_ok && i >= p.col_row_begin;
           const int cbuf = hook_cnt & 1;
 #pragma unroll
@@ -1208,6 +1216,8 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   // masked key tiles exist (causal, some row block ends before N): give them their own CTAs
   pp.fill_ctas = ((HOOK == kHookScores || HOOK == kHookScores16) && p.causal && p.p_seq + p.m_begin + 128 < p.N) ? 1 : 0;
   const int nslots = pp.fill_ctas ? 2 * ncb : ncb;
+  // the causal round-robin walk (down from the CTA's last key tile) is the reverse order: take its cheaper index form
+  if (pp.schedule == kRoundRobin && pp.causal) pp.schedule = kReverse;
   if (pp.n_splits < 1) pp.n_splits = 1;
   if (pp.n_splits == 1) pp.tiles_per_split = (p.N + BN - 1) / BN;
   dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B * pp.n_splits, nslots) : dim3(nslots, p.Hq, p.B * pp.n_splits);
