@@ -616,7 +616,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 
       // ---- score-tile hooks: off the chain above, they overlap this tile's P.V MMA
       if constexpr (HOOK == kHookRowSum) {
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // (packed 2 x fp32 adds measured 3 % slower here)
 #pragma unroll
         for (int x = 0; x < 128; x += 4) {
           s0 += FAWS_VIS(x) ? __uint_as_float(r[x]) : 0.f;
