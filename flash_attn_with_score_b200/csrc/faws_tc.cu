@@ -28,7 +28,11 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
+#include <cstring>
 #include <mutex>
+#include <queue>
+#include <vector>
 #include <type_traits>
 
 #include "faws_internal.cuh"
@@ -46,16 +50,16 @@ constexpr int MAX_KV_SLOTS = 4;
 constexpr int TMEM_COLS = 512;
 // setmaxnreg budget: the CTA is launched with 168 registers per thread (384 threads, one
 // CTA per SM); after re-allocation the total must not exceed that pool, otherwise the
-// .inc never returns.
+// .inc never returns.  88 / 208: with fewer registers for the producer and MMA warps their loops
+// spill (measured 2-3 % slower at 56 / 224), with 208 the softmax warps still do not.
 constexpr int REGS_LAUNCH = 168;
-constexpr int REGS_AUX = 56;
+constexpr int REGS_AUX = 88;
 constexpr int REGS_SOFTMAX = ((REGS_LAUNCH * NTHREADS - 128 * REGS_AUX) / 256) & ~7;
 static_assert(128 * REGS_AUX + 256 * REGS_SOFTMAX <= REGS_LAUNCH * NTHREADS, "setmaxnreg would block");
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #define FAWS_NEG_INF (__int_as_float(0xff800000))
-
 
 struct TcMaps {
   CUtensorMap q, k, v, o;  // o: 32-row store boxes of the output
@@ -83,6 +87,7 @@ struct Smem {
 
 struct Bars {
   uint64_t q_full;
+  uint64_t q_empty;       // persistent CTAs: the item's last Q.K^T has completed, the next item's Q tiles may land
   uint64_t kv_full[MAX_KV_SLOTS], kv_empty[MAX_KV_SLOTS];
   uint64_t s_full[2];     // per query tile: S_t written by the tensor pipe
   uint64_t p_half[2];     // per query tile: the first 64 columns of P_t are in TMEM
@@ -90,7 +95,6 @@ struct Bars {
   uint64_t col_ready[2];  // per query tile: column-sum partial rows of its 4 warps are in smem
   uint64_t o_done;        // every MMA of the CTA has completed
   uint64_t merge_ready;   // SPLIT: warpgroup 1 has published its (m, l, row sum)
-  uint64_t qsum_done;     // column hook: warps 2-3 have finished reading the Q tiles
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -140,9 +144,25 @@ enum Hook : int {
   kHookScores16 = 5  // scores in the input dtype (what the reference kernel writes)
 };
 
+// Persistent launches: one CTA per SM walks a list of work items (an item is what one CTA of the
+// plain launch does: a row block of one head), in the order of the plain launch's grid.  The
+// lists are made on the host (longest item first onto the least loaded CTA) and travel as a
+// kernel parameter, so that no device-side counter is shared between launches; launches with
+// more items than the lists hold deal the items to the CTAs in rounds of alternating direction.
+constexpr int kMaxListedItems = 2048;
+constexpr int kMaxListCtas = 192;
+struct WorkList {
+  int n_items;  // 0: plain launch, every CTA does the item its block index names
+  int listed;   // 1: CTA c does ids[start[c]] .. ids[start[c + 1] - 1]
+  int gx, gy, gz;  // the grid of the plain launch; an item is a linear block index of it (x fastest)
+  uint16_t start[kMaxListCtas + 1];
+  uint16_t ids[kMaxListedItems];
+};
+
 template <typename T, int D, int HOOK, bool SPLIT, bool DROP = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
-tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __restrict__ status) {
+tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __grid_constant__ WorkList wl,
+              int* __restrict__ status) {
   using L = Smem<D, SPLIT>;
   constexpr int KV_SLOTS = L::kSlots;
   constexpr int CTA_ROWS = L::kRows;
@@ -161,39 +181,64 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   // CTA and a fill CTA that only writes the row block's never-visited key tiles.  All compute
   // CTAs come first in launch order (heaviest first), the fill CTAs after them (most-masked row
   // block first): measured against interleaving the two kinds, cfg2 runs 2 % faster.
-  const int slot = (int)(p.lpt_order ? blockIdx.z : blockIdx.x);
-  const int ncb = (int)(p.lpt_order ? gridDim.z : gridDim.x) >> (p.fill_ctas ? 1 : 0);
-  const bool is_fill = p.fill_ctas && slot >= ncb;
-  const int cb_rel = is_fill ? slot - ncb : ncb - 1 - slot;  // compute: heaviest (last) blocks first
-  const int h = p.lpt_order ? blockIdx.x : blockIdx.y;
-  // Split-KV launches (n_splits > 1) fold the key-range index into the batch axis of the grid.
-  const int bz = p.lpt_order ? blockIdx.y : blockIdx.z;
-  const int b = bz / p.n_splits;
-  const int ksplit = bz - b * p.n_splits;
-  const int kt0 = ksplit * p.tiles_per_split;  // this CTA visits key tiles [kt0, kt0 + tiles_per_split)
-  const int hk = h / p.G;
-  const int bh = b * p.Hq + h;
-  const int ho = h * p.n_splits + ksplit;  // head index of the (partial) output this CTA writes
-
-  // first row of the CTA's query tile(s)
-  int r_tile_of[2];
-  r_tile_of[0] = p.m_begin + cb_rel * CTA_ROWS;
-  r_tile_of[1] = r_tile_of[0] + (SPLIT ? 0 : BM);
-  const int cb_abs = r_tile_of[0] / CTA_ROWS;  // start offset of the round-robin key-tile order
-
-  // key tiles each query tile visits (0 for a tile that lies outside the row window)
-  int nt_q[2];
+  // The geometry of the work item in hand.  Plain launches have one item per CTA, named by the block
+  // index; persistent CTAs (never SPLIT, split-KV or fill launches) set it again for every item.
+  const bool persist = !SPLIT && wl.n_items > 0;
+  bool is_fill;
+  int cb_rel, h, b, ksplit, kt0, hk, bh, ho, cb_abs, nt, rr_start;
+  int r_tile_of[2];  // first row of the item's query tile(s)
+  int nt_q[2];       // end of the key-tile range each query tile visits (kt0 for a tile outside the row window)
+  auto set_item = [&](int ix, int iy, int iz, int gx, int gz) {
+    const int slot = p.lpt_order ? iz : ix;
+    const int ncb = (p.lpt_order ? gz : gx) >> (p.fill_ctas ? 1 : 0);
+    is_fill = p.fill_ctas && slot >= ncb;
+    cb_rel = is_fill ? slot - ncb : ncb - 1 - slot;  // compute: heaviest (last) blocks first
+    h = p.lpt_order ? ix : iy;
+    // Split-KV launches (n_splits > 1) fold the key-range index into the batch axis of the grid.
+    const int bz = p.lpt_order ? iy : iz;
+    b = bz / p.n_splits;
+    ksplit = bz - b * p.n_splits;
+    kt0 = ksplit * p.tiles_per_split;  // the item visits key tiles [kt0, kt0 + tiles_per_split)
+    hk = h / p.G;
+    bh = b * p.Hq + h;
+    ho = h * p.n_splits + ksplit;  // head index of the (partial) output the item writes
+    r_tile_of[0] = p.m_begin + cb_rel * CTA_ROWS;
+    r_tile_of[1] = r_tile_of[0] + (SPLIT ? 0 : BM);
+    cb_abs = r_tile_of[0] / CTA_ROWS;  // start offset of the round-robin key-tile order
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int r0 = r_tile_of[t];
-    int hi = 0;
-    if (r0 < p.m_end) {
-      hi = p.N;
-      if (p.causal) hi = max(0, min(p.N, p.p_seq + min(r0 + BM, p.m_end)));
+    for (int t = 0; t < 2; ++t) {
+      const int r0 = r_tile_of[t];
+      int hi = 0;
+      if (r0 < p.m_end) {
+        hi = p.N;
+        if (p.causal) hi = max(0, min(p.N, p.p_seq + min(r0 + BM, p.m_end)));
+      }
+      nt_q[t] = min(max((hi + BN - 1) / BN, kt0), kt0 + p.tiles_per_split);
     }
-    nt_q[t] = min(max((hi + BN - 1) / BN, kt0), kt0 + p.tiles_per_split);  // end of the tile's key-tile range
-  }
-  const int nt = max(nt_q[0], nt_q[1]) - kt0;  // key tiles this CTA visits
+    nt = max(nt_q[0], nt_q[1]) - kt0;  // key tiles the item visits
+    rr_start = p.causal ? nt - 1 : cb_abs % max(nt, 1);
+  };
+  // k-th item of this CTA, or -1 when it has no more
+  auto item_at = [&](int k) -> int {
+    if (wl.listed) {
+      const int at = (int)wl.start[blockIdx.x] + k;
+      return at < (int)wl.start[blockIdx.x + 1] ? (int)wl.ids[at] : -1;
+    }
+    const int G = (int)gridDim.x;
+    const int idx = k * G + ((k & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return idx < wl.n_items ? idx : -1;
+  };
+  // moves on to the CTA's k-th item; false when there is none
+  auto goto_item = [&](int k) -> bool {
+    if (!persist) return false;  // (the first item of a plain launch is set below)
+    const int item = item_at(k);
+    if (item < 0) return false;
+    const int ix = item % wl.gx, rest = item / wl.gx;
+    set_item(ix, rest % wl.gy, rest / wl.gy, wl.gx, wl.gz);
+    return true;
+  };
+  if (persist) goto_item(0);
+  else set_item((int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)gridDim.x, (int)gridDim.z);
 
   if constexpr (HOOK == kHookScores || HOOK == kHookScores16) {
     if (is_fill) {
@@ -237,15 +282,15 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   // tile, the one only the second query tile visits, so that this lone step overlaps the CTA's set-up
   // instead of stalling the two-tile pipeline in mid-loop (a start in mid-range measured 10 % slower on
   // cfg3, an upward walk 5 %); the causal round-robin walk is then the reverse order itself.
-  const int rr_start = p.causal ? nt - 1 : cb_abs % max(nt, 1);
   auto tile_of = [&](int it) -> int {
     if (p.schedule == kReverse) return kt0 + nt - 1 - it;
     if (p.schedule == kRoundRobin) return kt0 + (rr_start - it + nt) % nt;
     return kt0 + it;
   };
   // K(0), V(0), K(1), V(1), ... go through the ring in this order
-  auto issue_kv_load = [&](int idx) {
-    const int s = idx % KV_SLOTS;
+  // (idx counts within the item, ring_idx over all items of the CTA)
+  auto issue_kv_load = [&](int idx, int ring_idx) {
+    const int s = ring_idx % KV_SLOTS;
     const int n0 = tile_of(idx >> 1) * BN;
     mbar_arrive_expect_tx(&bars->kv_full[s], L::kTile);
     const CUtensorMap* map = (idx & 1) ? &maps.v : &maps.k;
@@ -265,6 +310,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
   }
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_empty, HOOK == kHookColPart ? 3 : 1);  // the MMA warp (+ the two warps that sum the Q rows)
     for (int s = 0; s < KV_SLOTS; ++s) {
       mbar_init(&bars->kv_full[s], 1);
       mbar_init(&bars->kv_empty[s], 1);
@@ -277,7 +323,6 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     }
     mbar_init(&bars->o_done, 1);
     mbar_init(&bars->merge_ready, 128);
-    mbar_init(&bars->qsum_done, 64);
     bars->abort_flag = 0;
     mbar_fence_init();
     // This thread is also the TMA producer: start the first loads now so that their HBM
@@ -291,7 +336,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
                       r_tile_of[t] - p.m_begin, h, b);
-      for (int idx = 0; idx < n_early; ++idx) issue_kv_load(idx);
+      for (int idx = 0; idx < n_early; ++idx) issue_kv_load(idx, idx);
     }
   }
   if (warp == 1) {
@@ -312,18 +357,41 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     reg_dealloc<REGS_AUX>();
     if (warp == 0 && lane == 0) {
       // ---------------------------------------------------------- TMA producer (rest of the ring)
-      for (int idx = n_early; idx < 2 * nt; ++idx) {
-        const int s = idx % KV_SLOTS, u = idx / KV_SLOTS;
-        if (!mbar_wait(&bars->kv_empty[s], (u & 1) ^ 1, abort_flag)) break;
-        issue_kv_load(idx);
+      // Persistent CTAs: the ring runs on across items, so the next item's first K and V tiles arrive
+      // while the current item's last tiles are computed; its Q tiles follow as soon as the current
+      // item's last Q.K^T has completed.
+      int ring_base = 0;
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+        if (k > 0) {
+          if (!(ok = mbar_wait(&bars->q_empty, (k - 1) & 1, abort_flag))) break;
+          if (nt > 0) {
+            mbar_arrive_expect_tx(&bars->q_full, L::kQTiles * L::kTile);
+            for (int t = 0; t < L::kQTiles; ++t)
+              for (int c = 0; c < D / 64; ++c)
+                tma_load_4d(smem + L::q_off + t * L::kTile + c * L::kSub, &maps.q, &bars->q_full, c * 64,
+                            r_tile_of[t] - p.m_begin, h, b);
+          }
+        }
+        for (int idx = (k == 0 ? n_early : 0); idx < 2 * nt; ++idx) {
+          const int g = ring_base + idx;
+          const int s = g % KV_SLOTS, u = g / KV_SLOTS;
+          if (!(ok = mbar_wait(&bars->kv_empty[s], (u & 1) ^ 1, abort_flag))) break;
+          issue_kv_load(idx, g);
+        }
+        ring_base += 2 * nt;
+        if (!ok || !goto_item(k + 1)) break;
       }
     } else if (HOOK == kHookColPart && warp >= 2) {
       // ---------------------------------------------------------- per-tile sums of the query rows
       // The linear part of the raw column sums needs sum_i q_i of every fully contributing query
       // tile; the tiles are in shared memory anyway, so the two otherwise idle warps add them up.
       // A warp reads one 128-byte swizzled row segment per step (conflict-free).
+      int q_cnt = 0;  // items of this CTA whose Q tiles were loaded (those with key tiles to visit)
+      for (int k = 0;; ++k) {
+      if (nt > 0) ++q_cnt;
       if (p.col_lin != 0 && p.qsum != nullptr && nt > 0) {
-        if (mbar_wait(&bars->q_full, 0, abort_flag)) {
+        if (mbar_wait(&bars->q_full, (q_cnt - 1) & 1, abort_flag)) {
           const int nqb_total = (p.M + 127) / 128;
           for (int unit = (warp - 2) * 32 + lane; unit < L::kQTiles * (D / 2); unit += 64) {
             const int t = unit / (D / 2), pair = unit % (D / 2);
@@ -346,9 +414,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
             }
           }
         }
-        mbar_arrive(&bars->qsum_done);
       }
-    } else if (warp == 1 && nt > 0) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->q_empty);  // this warp no longer reads the item's Q tiles
+      // (its arrival for the next item must not be counted in this item's phase)
+      if (!persist || !mbar_wait(&bars->q_empty, k & 1, abort_flag) || !goto_item(k + 1)) break;
+      }
+    } else if (warp == 1) {
       // ---------------------------------------------------------- MMA issuer
       // The whole warp runs this loop (converged control flow); inside each group one elected
       // lane issues the tcgen05 instructions.
@@ -361,11 +433,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       const uint64_t q_desc0 = make_desc_sw128(smem_u32(smem + L::q_off), 16, 1024);
       const uint64_t k_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), 16, 1024);
       const uint64_t v_desc0 = make_desc_sw128(smem_u32(smem + L::kv_off), L::kSub, 1024);
+      int ring_base = 0;  // ring entries of the CTA's earlier items
       auto kv_wait = [&](int idx) -> bool {
-        if (!mbar_wait(&bars->kv_full[idx % KV_SLOTS], (idx / KV_SLOTS) & 1, abort_flag)) return false;
+        const int g = ring_base + idx;
+        if (!mbar_wait(&bars->kv_full[g % KV_SLOTS], (g / KV_SLOTS) & 1, abort_flag)) return false;
         tc_fence_after();
         return true;
       };
+      auto ring_slot = [&](int idx) -> int { return (ring_base + idx) % KV_SLOTS; };
       // S_t = Q_t . K^T for the key tile in ring slot `slot`
       auto issue_qk = [&](int t, int slot) {
         const uint64_t qd = q_desc0 + (uint64_t)((SPLIT ? 0 : t) * (L::kTile >> 4));
@@ -401,10 +476,11 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         __syncwarp();
       };
       // waits for the two hand-offs of query tile / warpgroup t and issues both halves
-      auto pv_when_ready = [&](int t, int slot, int c) -> bool {
+      // (c: hand-offs of t so far over all items, the barrier phase; first: is it the item's first)
+      auto pv_when_ready = [&](int t, int slot, int c, bool first) -> bool {
         if (!mbar_wait(&bars->p_half[t], c & 1, abort_flag)) return false;
         tc_fence_after();
-        issue_pv_half(t, slot, c > 0, 0);
+        issue_pv_half(t, slot, !first, 0);
         if (!mbar_wait(&bars->p_ready[t], c & 1, abort_flag)) return false;
         tc_fence_after();
         issue_pv_half(t, slot, true, 1);
@@ -428,8 +504,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if (elect_one()) mma_commit(bar);
         __syncwarp();
       };
-      int cnt[2] = {0, 0};  // key tiles each warpgroup has been given so far
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      int cnt[2] = {0, 0};  // key tiles each warpgroup has been given so far, over all items
+      int q_cnt = 0;        // items whose Q tiles were loaded
+      bool ok = true;
+      for (int k = 0; ok; ++k) {
+      if (nt > 0) {
+      ok = mbar_wait(&bars->q_full, q_cnt & 1, abort_flag);
+      ++q_cnt;
+      const int cnt0[2] = {cnt[0], cnt[1]};
       if constexpr (SPLIT) {
         // Visiting index `it` belongs to warpgroup it & 1.  Before S of that warpgroup is
         // overwritten by Q.K^T of tile it, the P.V of its previous tile (it - 2) is issued.
@@ -438,7 +520,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           if (it >= 2) {
             const int v_idx = 2 * (it - 2) + 1;
             if (!(ok = kv_wait(v_idx))) break;
-            if (!(ok = pv_when_ready(w, v_idx % KV_SLOTS, cnt[w]))) break;
+            if (!(ok = pv_when_ready(w, v_idx % KV_SLOTS, cnt[w], cnt[w] == cnt0[w]))) break;
             ++cnt[w];
             commit(&bars->kv_empty[v_idx % KV_SLOTS]);
           }
@@ -448,23 +530,24 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
             commit(&bars->kv_empty[(2 * it) % KV_SLOTS]);
           }
         }
-        ok = ok && true;
       } else {
       if (ok) ok = kv_wait(0);
       if (ok) {
         const int t0 = tile_of(0);
-        if (t0 < nt_q[0]) issue_qk(0, 0);
-        if (t0 < nt_q[1]) issue_qk(1, 0);
-        commit(&bars->kv_empty[0]);
+        if (t0 < nt_q[0]) issue_qk(0, ring_slot(0));
+        if (t0 < nt_q[1]) issue_qk(1, ring_slot(0));
+        commit(&bars->kv_empty[ring_slot(0)]);
       }
       for (int it = 0; ok && it < nt; ++it) {
         const int tk = tile_of(it);
         const bool more = it + 1 < nt;
         const int tk_next = more ? tile_of(it + 1) : 0;
-        const int v_slot = (2 * it + 1) % KV_SLOTS, k_slot = (2 * it + 2) % KV_SLOTS;
+        const int v_slot = ring_slot(2 * it + 1), k_slot = ring_slot(2 * it + 2);
+        // every Q.K^T of the item has been issued: when they complete, the next item's Q tiles may land
+        if (!more) commit(&bars->q_empty);
         if (!(ok = kv_wait(2 * it + 1))) break;
         if (tk < nt_q[0]) {
-          if (!(ok = pv_when_ready(0, v_slot, cnt[0]))) break;
+          if (!(ok = pv_when_ready(0, v_slot, cnt[0], cnt[0] == cnt0[0]))) break;
           ++cnt[0];
         }
         if (more) {
@@ -472,7 +555,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           if (tk_next < nt_q[0]) issue_qk(0, k_slot);
         }
         if (tk < nt_q[1]) {
-          if (!(ok = pv_when_ready(1, v_slot, cnt[1]))) break;
+          if (!(ok = pv_when_ready(1, v_slot, cnt[1], cnt[1] == cnt0[1]))) break;
           ++cnt[1];
         }
         commit(&bars->kv_empty[v_slot]);
@@ -483,6 +566,13 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       }
       }  // !SPLIT
       if (ok) commit(&bars->o_done);
+      ring_base += 2 * nt;
+      } else {  // an item without key tiles: nothing was loaded, nothing to issue
+        if (elect_one()) mbar_arrive(&bars->q_empty);
+        __syncwarp();
+      }
+      if (!ok || !goto_item(k + 1)) break;
+      }
     }
   } else {
     reg_alloc<REGS_SOFTMAX>();
@@ -490,13 +580,9 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     const int qt = (warp - 4) >> 2;  // warpgroup: its query tile (or, SPLIT, its half of the key tiles)
     const int lg = warp & 3;         // TMEM lane group this warp may touch
     const int row = lg * 32 + lane;
-    const int r_tile = r_tile_of[qt];  // first row of the query tile
-    const int i = r_tile + row;
-    const int my_nt = nt_q[qt];
     const uint32_t t_lane = tmem_base + ((uint32_t)(lg * 32) << 16);
     const uint32_t t_s = t_lane + (uint32_t)(qt * BN);
     const uint32_t t_o = t_lane + 256 + (uint32_t)(qt * BN);
-    const bool row_ok = i >= p.m_begin && i < p.m_end;
     const float scale = p.sm_scale;
     const float scale_log2 = p.sm_scale * kLog2e;
     unsigned char* stage = smem + L::stage_off + (warp - 4) * 8192;
@@ -504,15 +590,17 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
     constexpr bool store_scores = HOOK == kHookScores;
     constexpr bool store_scores16 = HOOK == kHookScores16;
     constexpr bool store_scratch = HOOK == kHookScratch;
-    const int qb128 = r_tile / BM;
-    const bool part_on = HOOK == kHookColPart && qb128 >= p.qb_first && r_tile < p.m_end;
     const float masked_f = __uint_as_float(p.masked_bits);
-    // Philox counter of (b, h, i, key 0) without the call's offset, 32-bit wrap-around
-    const uint32_t drop_row = ((uint32_t)bh * (uint32_t)p.M + (uint32_t)i) * (uint32_t)p.N;
-
-    float m_run = FAWS_NEG_INF, l_run = 0.f, rs_raw = 0.f;
+    // per item
+    int r_tile, i, my_nt, qb128;  // first row of the query tile, this thread's row, end of its key-tile range
+    bool row_ok, part_on;
+    uint32_t drop_row;  // Philox counter of (b, h, i, key 0) without the call's offset, 32-bit wrap-around
+    float m_run, l_run, rs_raw;
+    // over all items of the CTA
     bool alive = true;
     int hook_cnt = 0;  // column hook executions (selects its smem buffer and barrier phase)
+    int s_cnt = 0;     // key tiles processed (phase of s_full)
+    int o_cnt = 0;     // items with key tiles (phase of o_done)
 
     // One key tile.  The row's 128 scores are read from TMEM once and stay in registers: first
     // for the max and exp2 passes (the chain the tensor pipe waits on), then, after P has been
@@ -534,12 +622,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       // ---- row max (4 independent chains)
       float a0 = FAWS_NEG_INF, a1 = FAWS_NEG_INF, a2 = FAWS_NEG_INF, a3 = FAWS_NEG_INF;
 #pragma unroll
-      for (int x = 0; x < 128; x += 4) {
-        a0 = fmaxf(a0, FAWS_VIS(x) ? __uint_as_float(r[x]) : FAWS_NEG_INF);
-        a1 = fmaxf(a1, FAWS_VIS(x + 1) ? __uint_as_float(r[x + 1]) : FAWS_NEG_INF);
-        a2 = fmaxf(a2, FAWS_VIS(x + 2) ? __uint_as_float(r[x + 2]) : FAWS_NEG_INF);
-        a3 = fmaxf(a3, FAWS_VIS(x + 3) ? __uint_as_float(r[x + 3]) : FAWS_NEG_INF);
+#define FAWS_SV(x) (FAWS_VIS(x) ? __uint_as_float(r[x]) : FAWS_NEG_INF)
+      for (int x = 0; x < 128; x += 8) {  // three-input max: 64 instructions for 128 values
+        a0 = fmax3(a0, FAWS_SV(x), FAWS_SV(x + 1));
+        a1 = fmax3(a1, FAWS_SV(x + 2), FAWS_SV(x + 3));
+        a2 = fmax3(a2, FAWS_SV(x + 4), FAWS_SV(x + 5));
+        a3 = fmax3(a3, FAWS_SV(x + 6), FAWS_SV(x + 7));
       }
+#undef FAWS_SV
       const float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) * scale_log2;  // sm_scale > 0
 
       // ---- running max, lazy rescale of O.  s_full for this tile was committed after this
@@ -581,9 +671,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
           for (int y = 0; y < 8; y += 2) {
             const int x = c * 32 + g * 8 + y;
             float t0, t1;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2, neg_m2), t0, t1);
-            e[y] = FAWS_VIS(x) ? fast_exp2(t0) : 0.f;
-            e[y + 1] = FAWS_VIS(x + 1) ? fast_exp2(t1) : 0.f;
+            const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(r[x]), __uint_as_float(r[x + 1])), scale2, neg_m2);
+            unpack_f32x2(t2, t0, t1);
+            t0 = fast_exp2(t0);
+            t1 = fast_exp2(t1);
+            e[y] = FAWS_VIS(x) ? t0 : 0.f;
+            e[y + 1] = FAWS_VIS(x + 1) ? t1 : 0.f;
           }
           lp0 = add_f32x2(lp0, add_f32x2(pack_f32x2(e[0], e[1]), pack_f32x2(e[4], e[5])));
           lp1 = add_f32x2(lp1, add_f32x2(pack_f32x2(e[2], e[3]), pack_f32x2(e[6], e[7])));
@@ -738,6 +831,18 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       return true;
     };
 
+    for (int k = 0;; ++k) {
+    r_tile = r_tile_of[qt];
+    i = r_tile + row;
+    my_nt = nt_q[qt];
+    row_ok = i >= p.m_begin && i < p.m_end;
+    qb128 = r_tile / BM;
+    part_on = HOOK == kHookColPart && qb128 >= p.qb_first && r_tile < p.m_end;
+    drop_row = ((uint32_t)bh * (uint32_t)p.M + (uint32_t)i) * (uint32_t)p.N;
+    m_run = FAWS_NEG_INF;
+    l_run = 0.f;
+    rs_raw = 0.f;
+
     // Key tiles the causal loop never visits hold only the fill value.  They are written first,
     // from one constant 32 x 32 tile, so that HBM is busy while the first tiles are computed
     // (these stores carry 44 % of the bytes of a causal S = N problem).
@@ -782,7 +887,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         const int tk = tile_of(it);
         if (SPLIT ? ((it & 1) != qt) : (tk >= my_nt)) continue;
         const int n0 = tk * BN;
-        if (!mbar_wait(&bars->s_full[qt], cnt & 1, abort_flag)) { alive = false; break; }
+        if (!mbar_wait(&bars->s_full[qt], s_cnt & 1, abort_flag)) { alive = false; break; }
+        ++s_cnt;
         tc_fence_after();
         const bool full_vis = (n0 + BN <= p.N) && (!p.causal || (n0 + BN - 1 <= r_tile + p.p_seq));
         const bool ok = full_vis ? tile_body(std::false_type{}, cnt, n0) : tile_body(std::true_type{}, cnt, n0);
@@ -794,9 +900,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 
     // ---- epilogue: O / l -> out, log-normaliser, row sums, masked fill of unvisited tiles
     if (alive && my_nt > kt0) {
-      if (!mbar_wait(&bars->o_done, 0, abort_flag)) alive = false;
+      if (!mbar_wait(&bars->o_done, o_cnt & 1, abort_flag)) alive = false;
       tc_fence_after();
     }
+    if (nt > 0) ++o_cnt;
     // SPLIT: warpgroup 1 publishes its running state; warpgroup 0 merges the two partial results.
     float* merge = reinterpret_cast<float*>(smem + L::kv_off);  // ring is free after o_done
     bool write_out = alive && r_tile < p.m_end;
@@ -825,13 +932,37 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
       float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       if constexpr (DROP) inv *= p.drop.out_scale;
       if (my_nt > kt0) {
-        // Every MMA of the CTA has completed, so the Q tiles' shared memory is free: each warp
-        // stages its 32 x D output block there (128B-swizzled) and stores it with TMA.
-        unsigned char* ost = smem + L::q_off + (warp - 4) * (32 * D * 2);
-        if constexpr (HOOK == kHookColPart) {  // ... once warps 2-3 have summed the Q rows
-          if (p.col_lin != 0 && p.qsum != nullptr) mbar_wait(&bars->qsum_done, 0, abort_flag);
+        // Each warp stages its 32 x D output block (128B-swizzled) and stores it with TMA: in its own
+        // staging block where the hook leaves that free, so that a persistent CTA's next Q tiles can land
+        // meanwhile; in the Q tiles' shared memory (every MMA of the CTA has completed) under the hooks
+        // that stage score tiles.  The column hook keeps partial sums in the staging area: its rows go
+        // to global memory straight from the registers.
+        constexpr bool kDirect = HOOK == kHookColPart;
+        constexpr bool kOwnStage = HOOK == kHookNone || HOOK == kHookRowSum;
+        unsigned char* ost = kOwnStage ? stage : smem + L::q_off + (warp - 4) * (32 * D * 2);
+        T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + ho * p.o_sh + (int64_t)i * p.o_ss;
+        if (!kDirect && k > 0) {  // the previous item's store has read the staging block
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
         }
-        const float f0 = w0 * inv, f1 = w1 * inv;
+        [[maybe_unused]] const float f0 = w0 * inv, f1 = w1 * inv;
+        auto put_chunk = [&](int c, const uint32_t (&ro)[32]) {  // 32 columns of the row, already scaled
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(ro[g * 8 + 0]), __uint_as_float(ro[g * 8 + 1]));
+            w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]), __uint_as_float(ro[g * 8 + 3]));
+            w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]), __uint_as_float(ro[g * 8 + 5]));
+            w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]), __uint_as_float(ro[g * 8 + 7]));
+            if (kDirect) {
+              if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+            } else {
+              const int cc = (c & 1) * 4 + g;  // 16-byte chunk inside the 64-column sub-tile
+              *reinterpret_cast<uint4*>(ost + (c >> 1) * 4096 + lane * 128 + ((cc ^ (lane & 7)) << 4)) = w;
+            }
+          }
+        };
+        // (all D / 32 loads of the row in flight together measured 2-3 % slower: the registers they hold)
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t ro[32];
@@ -853,23 +984,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
 #pragma unroll
             for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * inv);
           }
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack2<T>(__uint_as_float(ro[g * 8 + 0]), __uint_as_float(ro[g * 8 + 1]));
-            w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]), __uint_as_float(ro[g * 8 + 3]));
-            w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]), __uint_as_float(ro[g * 8 + 5]));
-            w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]), __uint_as_float(ro[g * 8 + 7]));
-            const int cc = (c & 1) * 4 + g;  // 16-byte chunk inside the 64-column sub-tile
-            *reinterpret_cast<uint4*>(ost + (c >> 1) * 4096 + lane * 128 + ((cc ^ (lane & 7)) << 4)) = w;
-          }
+          put_chunk(c, ro);
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          for (int sub = 0; sub < D / 64; ++sub)
-            tma_store_4d(&maps.o, ost + sub * 4096, sub * 64, r_tile + lg * 32 - p.m_begin, ho, b);
-          tma_store_commit();
+        if (!kDirect) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            for (int sub = 0; sub < D / 64; ++sub)
+              tma_store_4d(&maps.o, ost + sub * 4096, sub * 64, r_tile + lg * 32 - p.m_begin, ho, b);
+            tma_store_commit();
+          }
         }
       } else if (row_ok) {
         // no key is visible to this query tile: its rows are zero
@@ -884,6 +1008,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, int* __res
         if constexpr (HOOK == kHookRowSum) p.row_sum[(int64_t)bh * p.M + i] = rs_all;
       }
     }
+    if (!alive || !goto_item(k + 1)) break;
+    }  // items of the CTA
     // Full completion, not only the reads: measured on the score-materialising launches, CTAs that leave
     // while their stores are still draining make the launch 4 % slower; no difference elsewhere.
     if (lane < 2) tma_store_wait<0>();
@@ -1202,6 +1328,85 @@ int* tc_status_word() {
 
 namespace {
 
+// Work lists of a persistent launch.  An item costs its key tiles plus a fixed part; the items, heaviest
+// first, go one by one to the CTA with the least work so far (what the hardware does with the CTAs of a
+// plain launch, here decided ahead).  Made once per problem geometry and kept for the next call.
+bool persistent_allowed();
+
+struct WorkKey {
+  int gx, gy, gz, lpt, causal, p_seq, m_begin, m_end, N, rows, ctas;
+  bool operator==(const WorkKey& o) const { return std::memcmp(this, &o, sizeof(WorkKey)) == 0; }
+};
+
+const WorkList& plain_work_list() {
+  static const WorkList wl{};  // n_items = 0
+  return wl;
+}
+
+// false: the launch should stay a plain one
+bool make_work_list(const FwdParams& p, dim3 grid, int cta_rows, int ctas, WorkList* out) {
+  const int n_items = (int)(grid.x * grid.y * grid.z);
+  if (ctas > kMaxListCtas || n_items <= ctas || n_items > 65535) return false;
+  const bool listed = n_items <= kMaxListedItems;
+  if (!listed && p.causal) return false;  // unequal items in no useful order: leave them to the hardware
+  thread_local WorkKey last_key{};
+  thread_local WorkList last{};
+  const WorkKey key{(int)grid.x, (int)grid.y, (int)grid.z, p.lpt_order, p.causal, p.p_seq, p.m_begin, p.m_end, p.N,
+                    cta_rows, ctas};
+  if (last.n_items > 0 && key == last_key) {
+    *out = last;
+    return true;
+  }
+  WorkList& wl = last;
+  wl = WorkList{};
+  wl.n_items = n_items;
+  wl.listed = listed ? 1 : 0;
+  wl.gx = (int)grid.x;
+  wl.gy = (int)grid.y;
+  wl.gz = (int)grid.z;
+  if (listed) {
+    const int ncb = (int)(p.lpt_order ? grid.z : grid.x);
+    std::vector<int> cost(ncb);
+    for (int slot = 0; slot < ncb; ++slot) {
+      const int r0 = p.m_begin + (ncb - 1 - slot) * cta_rows;
+      int tiles = 0;
+      for (int t = 0; t * BM < cta_rows; ++t) {
+        const int r = r0 + t * BM;
+        int hi = 0;
+        if (r < p.m_end) hi = p.causal ? std::max(0, std::min(p.N, p.p_seq + std::min(r + BM, p.m_end))) : p.N;
+        tiles = std::max(tiles, (hi + BN - 1) / BN);
+      }
+      cost[slot] = tiles + 2;  // fixed part: about two key tiles' time
+    }
+    auto cost_of = [&](int item) {
+      const int ix = item % wl.gx, iz = item / (wl.gx * wl.gy);
+      return cost[p.lpt_order ? iz : ix];
+    };
+    std::vector<int> order(n_items);
+    for (int i = 0; i < n_items; ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost_of(a) > cost_of(b); });
+    std::vector<std::vector<uint16_t>> mine(ctas);
+    using Load = std::pair<long long, int>;  // (work so far, CTA)
+    std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+    for (int c = 0; c < ctas; ++c) heap.push({0, c});
+    for (int item : order) {
+      Load l = heap.top();
+      heap.pop();
+      mine[l.second].push_back((uint16_t)item);
+      heap.push({l.first + cost_of(item), l.second});
+    }
+    int at = 0;
+    for (int c = 0; c < ctas; ++c) {
+      wl.start[c] = (uint16_t)at;
+      for (uint16_t id : mine[c]) wl.ids[at++] = id;
+    }
+    for (int c = ctas; c <= kMaxListCtas; ++c) wl.start[c] = (uint16_t)at;
+  }
+  last_key = key;
+  *out = wl;
+  return true;
+}
+
 template <typename T, int D, int HOOK, bool SPLIT, bool DROP = false>
 cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s) {
   using L = Smem<D, SPLIT>;
@@ -1221,6 +1426,16 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   if (pp.n_splits < 1) pp.n_splits = 1;
   if (pp.n_splits == 1) pp.tiles_per_split = (p.N + BN - 1) / BN;
   dim3 grid = pp.lpt_order ? dim3(p.Hq, p.B * pp.n_splits, nslots) : dim3(nslots, p.Hq, p.B * pp.n_splits);
+  // Tensor-bound launches with more items than SMs: one persistent CTA per SM walks a work list.
+  WorkList wl_persist;
+  const WorkList* wl = &plain_work_list();
+  if constexpr (!SPLIT && (HOOK == kHookNone || HOOK == kHookRowSum || HOOK == kHookColPart)) {
+    if (pp.n_splits == 1 && !pp.fill_ctas && persistent_allowed() &&
+        make_work_list(pp, grid, L::kRows, sm_count(), &wl_persist)) {
+      wl = &wl_persist;
+      grid = dim3(sm_count(), 1, 1);
+    }
+  }
   // Programmatic stream serialization: this launch may begin (CTA placement, barrier and TMEM set-up)
   // while the previous kernel of the stream drains; the kernel waits before any global access.
   cudaLaunchConfig_t cfg{};
@@ -1234,9 +1449,18 @@ cudaError_t launch_fwd_s(const TcMaps& maps, const FwdParams& p, cudaStream_t s)
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int* status_word = tc_status_word();
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>, maps, pp, status_word);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, tc_fwd_kernel<T, D, HOOK, SPLIT, DROP>, maps, pp, *wl, status_word);
   count_launch();
   return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+// FAWS_PERSISTENT=0 in the environment keeps every launch a plain one (tests, ablations).
+bool persistent_allowed() {
+  static const bool on = [] {
+    const char* e = std::getenv("FAWS_PERSISTENT");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
 }
 
 // Few CTAs (less than two per SM with 256-row CTAs): the launch is bound by the longest chain of

@@ -105,6 +105,38 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   return d;
 }
 
+__device__ __forceinline__ uint64_t add_rm_f32x2(uint64_t a, uint64_t b) {  // rounds towards -inf
+  uint64_t d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for two values on the FMA pipe instead of the special-function unit: x = n + f with
+// n = floor(x), 2^f from a cubic with relative error below 8.6e-5 on [0, 1) (less than half a
+// unit in the last place of a bf16 weight), n added to the exponent field.  x is clamped at
+// -126 so the result stays normal; inputs up to +127 are exact in n.
+__device__ __forceinline__ void exp2_poly_pair(uint64_t t, float& e0, float& e1) {
+  float a, b;
+  unpack_f32x2(t, a, b);
+  const uint64_t x = pack_f32x2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+  const uint64_t tm = add_rm_f32x2(x, pack_f32x2(12582912.f, 12582912.f));  // 1.5 * 2^23: low bits hold n
+  const uint64_t n = add_f32x2(tm, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.f, -1.f), x);
+  uint64_t pl = fma_f32x2(f, pack_f32x2(0.07706693559885025f, 0.07706693559885025f),
+                          pack_f32x2(0.2276451736688614f, 0.2276451736688614f));
+  pl = fma_f32x2(pl, f, pack_f32x2(0.6951166987419128f, 0.6951166987419128f));
+  pl = fma_f32x2(pl, f, pack_f32x2(1.f, 1.f));
+  float p0, p1, m0, m1;
+  unpack_f32x2(pl, p0, p1);
+  unpack_f32x2(tm, m0, m1);
+  e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(m0) << 23));
+  e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(m1) << 23));
+}
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
