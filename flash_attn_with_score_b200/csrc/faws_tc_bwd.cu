@@ -43,7 +43,7 @@ constexpr int NTHREADS = 384;
 constexpr int NSTAGE = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int REGS_LAUNCH = 168;
-constexpr int REGS_AUX = 56;
+constexpr int REGS_AUX = 88;
 constexpr int REGS_CONSUMER = ((REGS_LAUNCH * NTHREADS - 128 * REGS_AUX) / 256) & ~7;
 static_assert(128 * REGS_AUX + 256 * REGS_CONSUMER <= REGS_LAUNCH * NTHREADS, "setmaxnreg would block");
 constexpr float kLog2e = 1.4426950408889634f;
