@@ -51,7 +51,8 @@ constexpr int TMEM_COLS = 512;
 // setmaxnreg budget: the CTA is launched with 168 registers per thread (384 threads, one
 // CTA per SM); after re-allocation the total must not exceed that pool, otherwise the
 // .inc never returns.  88 / 208: with fewer registers for the producer and MMA warps their loops
-// spill (measured 2-3 % slower at 56 / 224), with 208 the softmax warps still do not.
+// spill (at 56 / 224 the score-materialising launch measured 5 % slower, the others 2-3 %); 104 / 200 and
+// 120 / 192 measured the same as 88 / 208.
 constexpr int REGS_LAUNCH = 168;
 constexpr int REGS_AUX = 88;
 constexpr int REGS_SOFTMAX = ((REGS_LAUNCH * NTHREADS - 128 * REGS_AUX) / 256) & ~7;
@@ -183,7 +184,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
   // block first): measured against interleaving the two kinds, cfg2 runs 2 % faster.
   // The geometry of the work item in hand.  Plain launches have one item per CTA, named by the block
   // index; persistent CTAs (never SPLIT, split-KV or fill launches) set it again for every item.
-  const bool persist = !SPLIT && wl.n_items > 0;
+  constexpr bool kStoreHook = HOOK == kHookScores || HOOK == kHookScores16 || HOOK == kHookScratch;
+  const bool persist = !SPLIT && !kStoreHook && wl.n_items > 0;  // (the launcher keeps the other instances plain)
   bool is_fill;
   int cb_rel, h, b, ksplit, kt0, hk, bh, ho, cb_abs, nt, rr_start;
   int r_tile_of[2];  // first row of the item's query tile(s)
