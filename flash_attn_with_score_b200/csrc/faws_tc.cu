@@ -1378,7 +1378,7 @@ bool make_work_list(const FwdParams& p, dim3 grid, int cta_rows, int ctas, WorkL
         if (r < p.m_end) hi = p.causal ? std::max(0, std::min(p.N, p.p_seq + std::min(r + BM, p.m_end))) : p.N;
         tiles = std::max(tiles, (hi + BN - 1) / BN);
       }
-      cost[slot] = tiles + 2;  // fixed part: about two key tiles' time
+      cost[slot] = tiles + 2;  // fixed part: about two key tiles' time (0 to 8 measured alike)
     }
     auto cost_of = [&](int item) {
       const int ix = item % wl.gx, iz = item / (wl.gx * wl.gy);
