@@ -182,6 +182,7 @@ int raw_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws
 struct SoftmaxWs {
   float* L;
   float* per_head;
+  float* negl;  // (B,Hq,M rounded up to 128): -L*log2e for the key-major tcgen05 kernel
   float* scratch;
   size_t total;
 };
@@ -194,6 +195,7 @@ SoftmaxWs carve_softmax_ws(const faws_problem* p, void* ws, int n_end, int split
   const size_t hbytes = align256((size_t)p->B * p->Hq * (size_t)n_end * 4);
   w.L = reinterpret_cast<float*>(base + off); off += lbytes;
   w.per_head = reinterpret_cast<float*>(base + off); off += hbytes;
+  w.negl = reinterpret_cast<float*>(base + off); off += align256((size_t)p->B * p->Hq * (size_t)(cdiv(p->M, 128) * 128) * 4);
   if (split_for_scratch > 0 && p->M > split_for_scratch) {
     w.scratch = reinterpret_cast<float*>(base + off);
     off += align256((size_t)p->B * p->Hq * (size_t)(p->M - split_for_scratch) * split_for_scratch * 4);
@@ -225,6 +227,10 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   if (w.scratch != nullptr) { c.s_scratch = w.scratch; c.split = buffered_split; }
   if (dropout_in_sum) c.drop = make_drop(p);
   c.after_forward = 1;
+  if (reinterpret_cast<uintptr_t>(w.negl) % 16 == 0) {  // bulk copies need 16-byte aligned sources
+    c.negl_pad = w.negl;
+    c.m_pad = cdiv(p->M, 128) * 128;
+  }
   if (i_begin >= p->m_end) {
     // no query of the window lies beyond the split: the sums are zero
     if (cudaMemsetAsync(sum_out, 0, (size_t)p->B * (per_q_head ? p->Hq : p->Hk) * (size_t)n_end * 4, s) != cudaSuccess)

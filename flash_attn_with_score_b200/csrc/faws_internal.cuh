@@ -119,6 +119,9 @@ struct ColSoftmaxParams {
   DropoutParams drop;    // p > 0: dropped weights are left out of the sum (no rescale)
   int after_forward;     // launched right after this call's forward pass, which wrote L but not q, k:
                          // the tcgen05 kernel may start its loads and MMAs while that pass drains
+  float* negl_pad;       // scratch (B,Hq,m_pad) or null: the tcgen05 launcher fills it with -L_i*log2e (-inf for
+                         // rows that do not contribute) and the kernel fetches it tile by tile with bulk copies
+  int m_pad;             // M rounded up to the query-tile height
 };
 
 struct ReducePartialParams {

@@ -1051,6 +1051,7 @@ constexpr int CS_KT = 2;
 constexpr int CS_WGS = 4;
 constexpr int CS_QSLOTS = CS_WGS;
 constexpr int CS_CHUNK = 64;  // score columns a consumer thread holds at a time
+constexpr int CS_LSLOTS = 8;  // query tiles whose -L values are in shared memory (see the producer)
 constexpr int CS_THREADS = 128 + CS_WGS * 128;
 constexpr int CS_REGS_LAUNCH = (65536 / CS_THREADS) & ~7;  // what the launch bound lets ptxas allocate
 constexpr int CS_REGS_AUX = 56;
@@ -1077,6 +1078,7 @@ struct CsBars {
   uint64_t q_full[CS_QSLOTS], q_empty[CS_QSLOTS];
   uint64_t s_full[CS_WGS], s_free[CS_WGS];  // per S^T buffer
   uint64_t l_ready[CS_WGS];
+  uint64_t l_full[CS_LSLOTS];  // -L*log2e of a query tile has landed (bulk copy from the padded array)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -1128,6 +1130,7 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       mbar_init(&bars->s_free[w], 128);
       mbar_init(&bars->l_ready[w], 128);
     }
+    for (int l = 0; l < CS_LSLOTS; ++l) mbar_init(&bars->l_full[l], 1);
     bars->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&maps.q);
@@ -1151,6 +1154,13 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
       for (int kt = 0; kt < CS_KT; ++kt)
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem + L::k_off + kt * L::kTile + c * L::kSub, &maps.k, &bars->k_full, c * 64, n0 + kt * BN, hk, b);
+      // -L_i*log2e of query tile u goes to slot u % 8 by one 512-byte bulk copy, issued after the Q load
+      // of tile u.  That load waited for the MMA of tile u - 4, which was issued only after both
+      // warpgroups of this parity had taken all of S^T of tile u - 6 out of TMEM, i.e. after they had
+      // finished tile u - 8: its slot is free.  The first copy waits for the kernel that wrote the
+      // array; the first Q loads (inputs of the whole call) are in flight by then.
+      int l_next = 0;
+      bool waited = false;
       for (int u = 0; u < total; ++u) {
         const int s = u % CS_QSLOTS, use = u / CS_QSLOTS;
         const int g = u / ntq, qt = qt0 + (u - g * ntq);
@@ -1159,6 +1169,19 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
         for (int c = 0; c < D / 64; ++c)
           tma_load_4d(smem + L::q_off + s * L::kTile + c * L::kSub, &maps.q, &bars->q_full[s], c * 64, qt * BM,
                       h0 + g, b);
+        if (p.negl_pad != nullptr && (u >= CS_QSLOTS - 1 || u == total - 1)) {
+          if (!waited) {
+            griddep_wait();
+            waited = true;
+          }
+          for (; l_next <= u; ++l_next) {
+            const int gl = l_next / ntq, ql = qt0 + (l_next - gl * ntq);
+            const int sl = l_next % CS_LSLOTS;
+            mbar_arrive_expect_tx(&bars->l_full[sl], BM * 4);
+            bulk_load_1d(lbuf + sl * BM, p.negl_pad + ((int64_t)b * p.Hq + h0 + gl) * p.m_pad + ql * BM, BM * 4,
+                         &bars->l_full[sl]);
+          }
+        }
       }
     } else if (warp == 1 && total > 0) {
       // ---------------------------------------------------------- MMA issuer: S^T = K . Q^T
@@ -1224,15 +1247,22 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
 
     bool alive = true;
     int mine = 0;  // tiles this warpgroup has processed
-    float negl_next = (par < total) ? load_negl(par) : FAWS_NEG_INF;
+    const bool padded = p.negl_pad != nullptr;  // the producer fetches -L*log2e; else the warpgroup loads L itself
+    float negl_next = (!padded && par < total) ? load_negl(par) : FAWS_NEG_INF;
     for (int u = par; u < total; u += 2, ++mine) {
-      // Two L buffers per warpgroup: the barrier below completes only when every thread of the
-      // warpgroup has finished the previous tile, so the buffer of the tile before that is free.
-      float* lb = lbuf + (wg * 2 + (mine & 1)) * 128;
-      lb[row] = negl_next;
-      mbar_arrive(&bars->l_ready[wg]);
-      if (u + 2 < total) negl_next = load_negl(u + 2);
-      if (!mbar_wait(&bars->l_ready[wg], mine & 1, abort_flag)) { alive = false; break; }
+      float* lb;
+      if (padded) {
+        lb = lbuf + (u % CS_LSLOTS) * BM;
+        if (!mbar_wait(&bars->l_full[u % CS_LSLOTS], (u / CS_LSLOTS) & 1, abort_flag)) { alive = false; break; }
+      } else {
+        // Two L buffers per warpgroup: the barrier below completes only when every thread of the
+        // warpgroup has finished the previous tile, so the buffer of the tile before that is free.
+        lb = lbuf + (wg * 2 + (mine & 1)) * 128;
+        lb[row] = negl_next;
+        mbar_arrive(&bars->l_ready[wg]);
+        if (u + 2 < total) negl_next = load_negl(u + 2);
+        if (!mbar_wait(&bars->l_ready[wg], mine & 1, abort_flag)) { alive = false; break; }
+      }
       if (!mbar_wait(&bars->s_full[wg], mine & 1, abort_flag)) { alive = false; break; }
       tc_fence_after();
       const int g = u / ntq, qt = qt0 + (u - g * ntq);
@@ -1613,6 +1643,43 @@ bool tc_colsoftmax_supported(const ColSoftmaxParams& p, int dtype) {
 }
 
 namespace {
+// -L_i*log2e into the tile-padded array the key-major kernel copies from; -inf for rows that do not
+// contribute (outside [i_lo, m_end), padding, or without a visible key).
+__global__ void negl_prep_kernel(const float* __restrict__ L, float* __restrict__ out, int M, int m_pad, int i_lo,
+                                 int m_end, long long total) {
+  griddep_wait();  // L comes from the forward pass before this launch
+  griddep_launch_dependents();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long bh = idx / m_pad;
+  const int i = (int)(idx - bh * m_pad);
+  float v = FAWS_NEG_INF;
+  if (i >= i_lo && i < m_end) {
+    const float Li = L[bh * M + i];
+    if (Li != FAWS_NEG_INF) v = -Li * kLog2e;
+  }
+  out[idx] = v;
+}
+
+cudaError_t launch_negl_prep(const ColSoftmaxParams& p, cudaStream_t s) {
+  const long long total = (long long)p.B * p.Hq * p.m_pad;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)((total + 255) / 256), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.after_forward ? 1 : 0;
+  const float* L = p.L;
+  float* out = p.negl_pad;
+  const int i_lo = p.i_begin > p.m_begin ? p.i_begin : p.m_begin;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, negl_prep_kernel, L, out, p.M, p.m_pad, i_lo, p.m_end, total);
+  count_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 template <typename T, int D>
 cudaError_t launch_cs_t(const CsMaps& maps, const ColSoftmaxParams& p, int heads_per_cta, cudaStream_t s) {
   using L = CsSmem<D>;
@@ -1645,6 +1712,9 @@ cudaError_t launch_tc_colsoftmax(const ColSoftmaxParams& p, int dtype, int group
       !make_map_bhsd(&maps.k, p.k, p.D, p.N, p.Hk, p.B, p.k_ss, p.k_sh, p.k_sb, 128))
     return cudaErrorInvalidValue;
   const int hpc = group_sum ? p.G : 1;
+  if (p.negl_pad != nullptr) {
+    if (cudaError_t e = launch_negl_prep(p, s); e != cudaSuccess) return e;
+  }
   if (dtype == FAWS_FP16)
     return p.D == 128 ? launch_cs_t<__half, 128>(maps, p, hpc, s) : launch_cs_t<__half, 64>(maps, p, hpc, s);
   return p.D == 128 ? launch_cs_t<__nv_bfloat16, 128>(maps, p, hpc, s)
