@@ -38,7 +38,7 @@ sys.path.insert(0, ROOT)
 CFG2 = dict(B=1, Hq=32, Hk=32, S=1024, D=128, dtype=torch.float16, causal=True)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on this
 # workload, from the committed ncu summary of that kernel on this workload (None = not captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 115_855_104  # 29.89 MB read + 85.97 MB written (the rest stays dirty in L2)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 112_927_744  # 25.48 MB read + 87.45 MB written (the rest stays dirty in L2)
 N_SETS = 4  # rotating buffer sets: 4 x (134 MB scores + 8 MB out + 25 MB inputs) > 126 MB of L2
 
 
