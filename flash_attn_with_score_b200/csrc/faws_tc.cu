@@ -812,6 +812,12 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
           const int cbuf = hook_cnt & 1;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
+            // a 32 x 32 block in which none of the warp's rows sees or contributes anything (above the
+            // diagonal, outside the row range) sums to zero without the 31 shuffles
+            if (!__any_sync(0xffffffffu, contrib && FAWS_VIS(c * 32))) {
+              colbuf[(cbuf * 4 + lg) * 128 + c * 32 + lane] = 0.f;
+              continue;
+            }
             float cv[32];
 #pragma unroll
             for (int x = 0; x < 32; ++x)
@@ -938,13 +944,14 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
         // Each warp stages its 32 x D output block (128B-swizzled) and stores it with TMA: in its own
         // staging block where the hook leaves that free, so that a persistent CTA's next Q tiles can land
         // meanwhile; in the Q tiles' shared memory (every MMA of the CTA has completed) under the hooks
-        // that stage score tiles.  The column hook keeps partial sums in the staging area: its rows go
-        // to global memory straight from the registers.
-        constexpr bool kDirect = HOOK == kHookColPart;
+        // that stage score tiles.  The column hook keeps partial sums in the first 4 KB of some warps'
+        // blocks: under it every warp stages 64 columns at a time in the upper 4 KB of its block
+        // (rows written straight from registers, 16 bytes per lane and instruction, measured 1.7 us per item).
+        constexpr bool kHalfStage = HOOK == kHookColPart;
         constexpr bool kOwnStage = HOOK == kHookNone || HOOK == kHookRowSum;
-        unsigned char* ost = kOwnStage ? stage : smem + L::q_off + (warp - 4) * (32 * D * 2);
-        T* orow = reinterpret_cast<T*>(p.o) + b * p.o_sb + ho * p.o_sh + (int64_t)i * p.o_ss;
-        if (!kDirect && k > 0) {  // the previous item's store has read the staging block
+        unsigned char* ost = kHalfStage ? stage + 4096
+                                        : (kOwnStage ? stage : smem + L::q_off + (warp - 4) * (32 * D * 2));
+        if (!kHalfStage && k > 0) {  // the previous item's store has read the staging block
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
         }
@@ -957,12 +964,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
             w.y = pack2<T>(__uint_as_float(ro[g * 8 + 2]), __uint_as_float(ro[g * 8 + 3]));
             w.z = pack2<T>(__uint_as_float(ro[g * 8 + 4]), __uint_as_float(ro[g * 8 + 5]));
             w.w = pack2<T>(__uint_as_float(ro[g * 8 + 6]), __uint_as_float(ro[g * 8 + 7]));
-            if (kDirect) {
-              if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
-            } else {
-              const int cc = (c & 1) * 4 + g;  // 16-byte chunk inside the 64-column sub-tile
-              *reinterpret_cast<uint4*>(ost + (c >> 1) * 4096 + lane * 128 + ((cc ^ (lane & 7)) << 4)) = w;
-            }
+            const int cc = (c & 1) * 4 + g;  // 16-byte chunk inside the 64-column sub-tile
+            *reinterpret_cast<uint4*>(ost + (kHalfStage ? 0 : (c >> 1) * 4096) + lane * 128 + ((cc ^ (lane & 7)) << 4)) = w;
           }
         };
         // (all D / 32 loads of the row in flight together measured 2-3 % slower: the registers they hold)
@@ -970,6 +973,10 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
         for (int c = 0; c < D / 32; ++c) {
           uint32_t ro[32];
           tmem_ld32(t_o + c * 32, ro);
+          if (kHalfStage && (c & 1) == 0 && (c > 0 || k > 0)) {  // the store before this one has read the half block
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+          }
           tmem_wait_ld();
           if constexpr (SPLIT) {
             if (have1) {
@@ -988,8 +995,16 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
             for (int x = 0; x < 32; ++x) ro[x] = __float_as_uint(__uint_as_float(ro[x]) * inv);
           }
           put_chunk(c, ro);
+          if (kHalfStage && (c & 1) == 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_4d(&maps.o, ost, (c >> 1) * 64, r_tile + lg * 32 - p.m_begin, ho, b);
+              tma_store_commit();
+            }
+          }
         }
-        if (!kDirect) {
+        if (!kHalfStage) {
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
