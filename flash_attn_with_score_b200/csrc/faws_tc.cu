@@ -1434,11 +1434,11 @@ bool make_work_list(const FwdParams& p, dim3 grid, int cta_rows, int ctas, WorkL
     for (int i = 0; i < n_items; ++i) order[i] = i;
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost_of(a) > cost_of(b); });
     // Heaviest item first onto the CTA with the least work so far (what the hardware does with the CTAs
-    // of a plain grid), then exchanges of single items between the fullest CTA and any other that lower
-    // the fuller of the two.  Exchanges keep the number of items per CTA, so the result does not lean on
-    // the fixed cost per item, which differs between the hooks (3 us plain, 8 us with the column hook,
-    // measured on cfg3; packing to a capacity instead put up to 30 small items on one CTA and was 30 %
-    // slower under the column hook).  cfg3: fullest CTA 56 -> 54 key tiles at a mean of 51.5.
+    // of a plain grid), then exchanges of single items between any two CTAs that bring their loads closer
+    // together, fuller CTAs first against the emptiest.  Exchanges keep the number of items per CTA, so
+    // the result does not lean on the fixed cost per item, which differs between the hooks (3 us plain,
+    // 6 us with the column hook, measured on cfg3; packing to a capacity instead put up to 30 small items
+    // on one CTA and was 30 % slower under the column hook).  cfg3: 48..56 key tiles per CTA -> 50..52.
     std::vector<std::vector<uint16_t>> mine(ctas);
     std::vector<long long> load(ctas, 0);
     {
@@ -1453,27 +1453,35 @@ bool make_work_list(const FwdParams& p, dim3 grid, int cta_rows, int ctas, WorkL
         heap.push({load[l.second], l.second});
       }
     }
-    for (int round = 0; round < 4 * ctas; ++round) {
-      int A = 0;
-      for (int c = 1; c < ctas; ++c)
-        if (load[c] > load[A]) A = c;
-      long long best = load[A];
-      int bB = -1, bia = 0, bib = 0;
-      for (int B = 0; B < ctas; ++B) {
-        if (B == A || load[B] >= load[A]) continue;
-        for (size_t ia = 0; ia < mine[A].size(); ++ia)
-          for (size_t ib = 0; ib < mine[B].size(); ++ib) {
-            const long long d = cost_of(mine[A][ia]) - cost_of(mine[B][ib]);
-            if (d <= 0) continue;
-            const long long worst = std::max(load[A] - d, load[B] + d);
-            if (worst < best) { best = worst; bB = B; bia = (int)ia; bib = (int)ib; }
-          }
+    for (int round = 0; round < 32; ++round) {
+      bool improved = false;
+      std::vector<int> by_load(ctas);
+      for (int c = 0; c < ctas; ++c) by_load[c] = c;
+      std::stable_sort(by_load.begin(), by_load.end(), [&](int x, int y) { return load[x] > load[y]; });
+      for (int ai = 0; ai < ctas; ++ai) {
+        const int A = by_load[ai];
+        for (int bi = ctas - 1; bi >= 0; --bi) {
+          const int B = by_load[bi];
+          const long long gap = load[A] - load[B];
+          if (gap <= 0) break;  // (the order is the one before this round's exchanges: good enough)
+          long long best_gain = 0, best_d = 0;
+          int bia = -1, bib = -1;
+          for (size_t ia = 0; ia < mine[A].size(); ++ia)
+            for (size_t ib = 0; ib < mine[B].size(); ++ib) {
+              const long long d = cost_of(mine[A][ia]) - cost_of(mine[B][ib]);
+              if (d <= 0 || d >= gap) continue;
+              const long long after = gap - 2 * d;
+              const long long gain = gap - (after < 0 ? -after : after);  // how much closer the two get
+              if (gain > best_gain) { best_gain = gain; best_d = d; bia = (int)ia; bib = (int)ib; }
+            }
+          if (bia < 0) continue;
+          std::swap(mine[A][bia], mine[B][bib]);
+          load[A] -= best_d;
+          load[B] += best_d;
+          improved = true;
+        }
       }
-      if (bB < 0) break;
-      const long long d = cost_of(mine[A][bia]) - cost_of(mine[bB][bib]);
-      std::swap(mine[A][bia], mine[bB][bib]);
-      load[A] -= d;
-      load[bB] += d;
+      if (!improved) break;
     }
     for (int c = 0; c < ctas; ++c)  // heaviest item first within a CTA
       std::stable_sort(mine[c].begin(), mine[c].end(), [&](uint16_t x, uint16_t y) { return cost_of(x) > cost_of(y); });
