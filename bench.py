@@ -498,9 +498,9 @@ def query_split_leg(F, device, rank, world, pk):
         for b in range(cfg["B"]):
             F.attention_with_softmax_col_sum(q[b:b + 1], k[b:b + 1], v[b:b + 1], False, q_rows=(begin, end))
 
-    ms = _time_calls(run_overlap, steps, 1, device, world)
-    ms_serial = _time_calls(run_serial, steps, 1, device, world)
-    ms_compute = _time_calls(run_compute_only, steps, 1, device, world)
+    ms = _time_calls(run_overlap, steps, 2, device, world)
+    ms_serial = _time_calls(run_serial, steps, 2, device, world)
+    ms_compute = _time_calls(run_compute_only, steps, 2, device, world)
     out, sums, rows = res["v"]
     # parity that is not rank-vs-rank: mass conservation per (b, kv head), and one kv head against the unsplit call
     total = sums.double().sum(-1)
@@ -521,7 +521,7 @@ def query_split_leg(F, device, rank, world, pk):
     return {"workload": "cfg5", "op": "attention_with_softmax_col_sum", "scaling": "strong", "n_gpus": world,
             "ms_per_step": ms, "ms_per_step_exchange_after_compute": ms_serial,
             "ms_per_step_exchange_overlapped_per_batch_element": ms_overlap, "ms_compute_only": ms_compute,
-            "exposed_exchange_ms": max(0.0, ms_serial - ms_compute),
+            "exposed_exchange_ms": max(0.0, ms - ms_compute),  # of the form the headline uses
             "tflops": flops / (ms * 1e-3) / 1e12, "steps": steps, "rows_per_rank": rows[1] - rows[0],
             "collective": "all_gather of the fp32 partial column sums + fixed-order reduce kernel, after the compute "
                           "(whole batch) or per batch element overlapping the next element's kernels; the faster is "
