@@ -663,9 +663,18 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
       const uint64_t neg_m2 = pack_f32x2(neg_m, neg_m);
       const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
       uint64_t lp0 = 0ull, lp1 = 0ull;
+      // masked tiles: the most columns any row of this warp sees (a 32-column block beyond it is all
+      // zeros in P for the whole warp and skips its 32 exponentials per row: 6 of the 16 blocks of a
+      // diagonal tile)
+      const int nvis_warp = kMasked ? __reduce_max_sync(0xffffffffu, nvis) : 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
+        const bool block_hidden = kMasked && c * 32 >= nvis_warp;
+        if (block_hidden) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) pk[x] = 0u;
+        } else {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float e[8];
@@ -695,6 +704,7 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
           pk[g * 4 + 1] = pack2<T>(e[2], e[3]);
           pk[g * 4 + 2] = pack2<T>(e[4], e[5]);
           pk[g * 4 + 3] = pack2<T>(e[6], e[7]);
+        }
         }
         tmem_st16(t_s + c * 16, pk);
         if (c == 1) {  // first 64 key columns of P are complete: let their P.V K-steps start
