@@ -1327,8 +1327,11 @@ tc_colsoftmax_kernel(const __grid_constant__ CsMaps maps, const ColSoftmaxParams
           unpack_f32x2(ap1, a2, a3);
         } else {
           const int xh = xlo - c0;
+          // query columns below the smallest bound in the warp are hidden from all of its keys: no exp2 there
+          const int xh_warp = __reduce_min_sync(0xffffffffu, xh);
 #pragma unroll
           for (int x = 0; x < CS_CHUNK; x += 4) {
+            if (x + 3 < xh_warp) continue;
             const float4 nl = *reinterpret_cast<const float4*>(lh + x);
             a0 += (x >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x]), scale_log2, nl.x)) : 0.f;
             a1 += (x + 1 >= xh) ? fast_exp2(fmaf(__uint_as_float(r[x + 1]), scale_log2, nl.y)) : 0.f;
