@@ -63,6 +63,10 @@ FwdParams make_fwd(const faws_problem* p) {
   return f;
 }
 
+// Scratch must start on a 256-byte boundary (faws_workspace_bytes says so): the kernels read and write it with
+// 16-byte vectors, TMA stores and bulk copies.
+bool misaligned_ws(const void* ws) { return reinterpret_cast<uintptr_t>(ws) % 256 != 0; }
+
 ColSoftmaxParams make_cs(const faws_problem* p, const float* L, float* out, int i_begin, int n_end) {
   ColSoftmaxParams c{};
   c.q = p->q.ptr; c.k = p->k.ptr;
@@ -153,7 +157,7 @@ int raw_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void* ws
   if (sum_out == nullptr) return FAWS_EINVAL;
   const size_t part_bytes = align256(partial_floats(p, row_begin, n_end) * 4);
   const size_t need = part_bytes + align256(qsum_floats(p) * 4);
-  if (ws == nullptr || ws_bytes < need) return FAWS_EWORKSPACE;
+  if (ws == nullptr || ws_bytes < need || misaligned_ws(ws)) return FAWS_EWORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   FwdParams f = make_fwd(p);
   f.schedule = schedule;
@@ -213,7 +217,7 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   if (st != FAWS_OK) return st;
   if (sum_out == nullptr) return FAWS_EINVAL;
   SoftmaxWs w = carve_softmax_ws(p, nullptr, n_end, buffered_split);
-  if (ws == nullptr || ws_bytes < w.total) return FAWS_EWORKSPACE;
+  if (ws == nullptr || ws_bytes < w.total || misaligned_ws(ws)) return FAWS_EWORKSPACE;
   w = carve_softmax_ws(p, ws, n_end, buffered_split);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   FwdParams f = make_fwd(p);
@@ -227,10 +231,8 @@ int softmax_col_sums(const faws_problem* p, float* sum_out, int per_q_head, void
   if (w.scratch != nullptr) { c.s_scratch = w.scratch; c.split = buffered_split; }
   if (dropout_in_sum) c.drop = make_drop(p);
   c.after_forward = 1;
-  if (reinterpret_cast<uintptr_t>(w.negl) % 16 == 0) {  // bulk copies need 16-byte aligned sources
-    c.negl_pad = w.negl;
-    c.m_pad = cdiv(p->M, 128) * 128;
-  }
+  c.negl_pad = w.negl;  // (16-byte aligned like every region of the scratch: bulk copies read it)
+  c.m_pad = cdiv(p->M, 128) * 128;
   if (i_begin >= p->m_end) {
     // no query of the window lies beyond the split: the sums are zero
     if (cudaMemsetAsync(sum_out, 0, (size_t)p->B * (per_q_head ? p->Hq : p->Hk) * (size_t)n_end * 4, s) != cudaSuccess)
@@ -354,7 +356,8 @@ int faws_attention_split_kv(const faws_problem* p, int32_t n_splits, void* works
   if (p->dropout_p > 0.f) return FAWS_EUNSUPPORTED;  // the reference refuses dropout with split-KV too (flash.py:98)
   if (p->m_begin != 0 || p->m_end != p->M) return FAWS_EINVAL;
   if (n_splits == 1) return faws_attention(p, stream);
-  if (workspace == nullptr || workspace_bytes < split_kv_bytes(p, n_splits)) return FAWS_EWORKSPACE;
+  if (workspace == nullptr || workspace_bytes < split_kv_bytes(p, n_splits) || misaligned_ws(workspace))
+    return FAWS_EWORKSPACE;
   if (p->out.ptr == nullptr || p->v.ptr == nullptr) return FAWS_EINVAL;
   faws_problem packed;  // same bytes of workspace either way: B*Hq*M is unchanged by the packing
   if (p->backend != FAWS_BACKEND_GENERIC && pack_gqa(p, &packed)) {
@@ -479,7 +482,7 @@ int faws_attention_backward(const faws_problem* p, const faws_grads* g, void* wo
     return FAWS_EINVAL;
   if (p->m_begin != 0 || p->m_end != p->M) return FAWS_EINVAL;
   const size_t need = faws_workspace_bytes(FAWS_OP_ATTENTION_BACKWARD, p, 0);
-  if (workspace == nullptr || workspace_bytes < need) return FAWS_EWORKSPACE;
+  if (workspace == nullptr || workspace_bytes < need || misaligned_ws(workspace)) return FAWS_EWORKSPACE;
   BwdParams b{};
   b.q = p->q.ptr; b.k = p->k.ptr; b.v = p->v.ptr; b.o = p->out.ptr;
   b.dout = g->dout.ptr; b.dq = g->dq.ptr; b.dk = g->dk.ptr; b.dv = g->dv.ptr;

@@ -57,6 +57,17 @@ def test_validation_without_gpu(lib):
     p.philox_offset = 2 ** 31
     assert lib.faws_attention(C.byref(p), None) == -2  # 64-bit Philox variant
     p.dropout_p = 0.0
+    # scratch that is missing, too small or not on a 256-byte boundary is refused before anything is launched
+    p.Hq, p.Hk, p.m_begin, p.m_end, p.sm_scale = 4, 2, 0, 8, 0.125
+    for t in (p.q, p.k, p.v, p.out):  # fake addresses, never dereferenced: the checks below come first
+        t.ptr, t.stride_b, t.stride_h, t.stride_s = 1 << 21, 4 * 8 * 64, 8 * 64, 64
+    need = lib.faws_workspace_bytes(5, C.byref(p), 0)
+    assert need > 0 and need % 256 == 0
+    fake_sum, fake_ws = C.c_void_p(4096), 1 << 20  # never dereferenced: the checks come first
+    assert lib.faws_attention_with_softmax_col_sum(C.byref(p), fake_sum, 0, None, need, None) == -3
+    assert lib.faws_attention_with_softmax_col_sum(C.byref(p), fake_sum, 0, C.c_void_p(fake_ws), need - 1, None) == -3
+    assert lib.faws_attention_with_softmax_col_sum(C.byref(p), fake_sum, 0, C.c_void_p(fake_ws + 16), need, None) == -3
+    assert lib.faws_attention_with_col_sum(C.byref(p), fake_sum, 0, C.c_void_p(fake_ws + 64), 1 << 30, None) == -3
     assert b"workspace" in lib.faws_strerror(-3)
     assert lib.faws_reduce_ranks(None, 2, 4, None, None) == -1
 
