@@ -562,7 +562,7 @@ const char* faws_strerror(int status) {
     case FAWS_OK: return "ok";
     case FAWS_EINVAL: return "invalid argument (shape, pointer, window or split)";
     case FAWS_EUNSUPPORTED: return "unsupported head dimension or dtype";
-    case FAWS_EWORKSPACE: return "workspace missing or too small";
+    case FAWS_EWORKSPACE: return "workspace missing, too small or not on a 256-byte boundary";
     case FAWS_ECUDA: return "CUDA call failed";
     case FAWS_EBACKEND: return "requested kernel family cannot run this problem";
     case FAWS_ETOOLARGE: return "problem needs more scratch than the built-in array of the _noalloc entry point";

@@ -40,7 +40,7 @@ extern "C" {
 #define FAWS_OK 0
 #define FAWS_EINVAL (-1)      /* bad shape, NULL pointer, split out of range  */
 #define FAWS_EUNSUPPORTED (-2) /* head dim / dtype / alignment not supported  */
-#define FAWS_EWORKSPACE (-3)  /* workspace missing or too small               */
+#define FAWS_EWORKSPACE (-3)  /* workspace missing, too small or misaligned   */
 #define FAWS_ECUDA (-4)       /* a CUDA runtime / driver call failed          */
 #define FAWS_EBACKEND (-5)    /* forced backend cannot run this problem       */
 #define FAWS_ETOOLARGE (-6)   /* problem exceeds the built-in scratch of the  */
