@@ -42,7 +42,11 @@ out, cs = F.attention_with_col_sum(q, k, v, causal, q_rows=q_rows)
 res["col_sum.out"], res["col_sum"] = out, cs
 out, cs = F.attention_with_col_sum_sequential(q, k, v, causal, q_rows=q_rows)
 res["col_seq.out"], res["col_seq"] = out, cs
+out, cs = F.attention_with_softmax_col_sum(q, k, v, causal, q_rows=q_rows)
+res["softmax_col_sum.out"], res["softmax_col_sum"] = out, cs
 if M == N and q_rows is None:
+    out, x = F.attention_cross_token_softmax_sum(q, k, v, N // 2, causal)
+    res["cross_softmax.out"], res["cross_softmax"] = out, x
     out, x = F.attention_cross_token_qk_sum(q, k, v, N // 2, causal)
     res["cross_qk.out"], res["cross_qk"] = out, x
     out = F.attention(q, k, v, causal, dropout_p=0.25, philox=(1234, 77))
