@@ -398,6 +398,8 @@ tc_fwd_kernel(const __grid_constant__ TcMaps maps, const FwdParams p, const __gr
           const int nqb_total = (p.M + 127) / 128;
           for (int unit = (warp - 2) * 32 + lane; unit < L::kQTiles * (D / 2); unit += 64) {
             const int t = unit / (D / 2), pair = unit % (D / 2);
+            // (a tile that starts before the first contributing row is never a linear one: its sum is not read)
+            if (r_tile_of[t] < p.col_row_lo) continue;
             const int c = pair >> 5, word = pair & 31;
             const unsigned char* base = smem + L::q_off + t * L::kTile + c * L::kSub + ((word & 3) << 2);
             float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
