@@ -21,6 +21,9 @@ CASES = [
     ("listed_window", 1, 24, 8, 2048, 2304, 128, "bfloat16", True, (256, 1920)),  # M != N, row window
     ("listed_full_d64", 2, 16, 16, 1536, 1280, 64, "float16", False, None),    # equal items, 192 of them
     ("rounds_full", 4, 32, 8, 4352, 512, 64, "bfloat16", False, None),         # 2176 items: dealt in rounds
+    ("ragged_causal_d64", 2, 12, 4, 1900, 2100, 64, "bfloat16", True, None),   # M, N off the tile grid
+    ("m_gt_n_causal", 1, 20, 4, 2304, 1800, 128, "float16", True, None),       # first row blocks see no key at all
+    ("gqa_window_full", 1, 40, 8, 1100, 900, 128, "float16", False, (128, 1024)),
 ]
 
 CHILD = r"""
@@ -93,11 +96,14 @@ def test_persistent_launch_equals_plain_launch(case, tmp_path):
         i = torch.arange(M)[:, None]
         j = torch.arange(N)[None, :]
         s = s.masked_fill(j > i + (N - M), float("-inf"))
-    ref = torch.softmax(s, -1) @ v[-1, hk].float()
+    seen = ~torch.isinf(s).all(-1)  # rows that see at least one key; the others are zero rows in the output
+    ref = torch.softmax(s.masked_fill(~seen[:, None], 0.0), -1) @ v[-1, hk].float()
+    ref[~seen] = 0.0
     lo, hi = q_rows if q_rows is not None else (0, M)
     got = pers["attention.out"][-1, h].float()  # (the saved tensors hold the window's rows only)
     tol = 2e-3 if dt == torch.float16 else 1.6e-2  # half a unit in the last place of the 16-bit output at |out| <= 4, doubled
     assert (got - ref[lo:hi]).abs().max().item() <= tol
+    assert got[~seen[lo:hi]].abs().max().item() == 0.0 if (~seen[lo:hi]).any() else True
     want_rs = torch.where(torch.isinf(s), torch.zeros_like(s), s).sum(-1)
     rs = pers["row_sum"][-1, h]
     assert torch.allclose(rs, want_rs[lo:hi], rtol=2e-3, atol=2e-2)
