@@ -107,3 +107,29 @@ def test_persistent_launch_equals_plain_launch(case, tmp_path):
     want_rs = torch.where(torch.isinf(s), torch.zeros_like(s), s).sum(-1)
     rs = pers["row_sum"][-1, h]
     assert torch.allclose(rs, want_rs[lo:hi], rtol=2e-3, atol=2e-2)
+
+
+def test_persistent_launch_replays_from_a_cuda_graph():
+    """The work lists travel as a kernel parameter, so a captured persistent launch replays with them."""
+    import flash_attn_with_score_b200 as F
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(3)
+    q = torch.randn(2, 16, 2048, 128, device=dev, dtype=torch.float16, generator=g)  # 256 work items
+    k = torch.randn(2, 4, 2048, 128, device=dev, dtype=torch.float16, generator=g)
+    v = torch.randn(2, 4, 2048, 128, device=dev, dtype=torch.float16, generator=g)
+    want_out, want_rs = F.attention_with_row_sum(q, k, v, True)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        got_out, got_rs = F.attention_with_row_sum(q, k, v, True)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        got_out.zero_()
+        got_rs.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(got_out, want_out)
+        assert torch.equal(got_rs, want_rs)
+    assert F.device_status() == 0
