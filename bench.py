@@ -308,7 +308,13 @@ def extra_rows(F, device, pk):
     ms = time_op(lambda: F.compute_attention_scores(q, k), 30, 3)
     n = CFG2["Hq"] * CFG2["S"]
     add("cfg2", "compute_attention_scores", ms, 2 * n * CFG2["S"] * CFG2["D"], 2 * n * CFG2["D"] * 2 + n * CFG2["S"] * 2)
-    del q, k
+    # the headline operator with scores in the input dtype and zeros at hidden entries: what the reference's own
+    # kernel writes (attention_with_scores.py:141-152,284); half the score bytes of the fp32 form
+    q, k, v = make_inputs(CFG2, 0, device)
+    ms = time_op(lambda: F.attention_with_scores(q, k, v, True, scores_dtype=q.dtype, masked_value=0.0), 30, 3)
+    flops, nbytes = algorithmic(CFG2, "scores", None)
+    add("cfg2", "attention_with_scores (16-bit scores)", ms, flops, nbytes - n * CFG2["S"] * 2)
+    del q, k, v
 
     # decoding: few query rows against 16 384 keys; K/V traffic bounds it.  The G = 4 query heads of a kv head are
     # packed into one query tile (K and V stream once per kv head) and the keys are cut into ranges (split-KV).
